@@ -190,6 +190,9 @@ class Engine {
   struct StackWs {
     float *x, *p1, *p2, *cq, *qabs, *ctx, *mo, *y;
     bf16 *x16, *cq16, *mo16;
+    float* hn = nullptr;      // HB_NORM_BOTH_SIDES: the normed input of the current sublayer [T][width] (x16 is then ITS bf16 copy)
+    float* y2 = nullptr;      // mixture of experts with a unit every token uses: that unit's output [T][width]
+    float* vfirst = nullptr;  // blended values: the first blending layer's values of the step's tokens [T][kv_heads * vdim]
     int ld1, ld2, ldcq, ldqa, ldctx, ldmo;
     // attention of long prompt portions as dense products (bf16 mode): bf16 queries, gathered keys, scores, probabilities
     bf16 *q16 = nullptr, *ctx16 = nullptr;  // bf16 copies of the per-head queries / weighted latents (per-head tcgen05 products)

@@ -1,4 +1,4 @@
-// Layer-list decoders (HB_ARCH_STACK: the Risepel and Lurepel designs) inside hb::Engine: model load, the page pool's planes and recurrent state slots,
+// Layer-list decoders (HB_ARCH_STACK: the Risepel, Lurepel and Latanex designs) inside hb::Engine: model load, the page pool's planes and recurrent state slots,
 // the step's forward pass and the driven-sequence entry points.  Scheduling, page bookkeeping, the step block, sampling
 // and request records are the engine's own (engine.cu); this file adds what differs from the Llama path:
 //   * the residual stream is fp32 and post-normed; every sublayer reads the stream itself;
@@ -152,6 +152,10 @@ static size_t stack_skinny_floats(const Model& m) {
       shape(2 * (size_t)l.ff, W);
       shape(W, l.ff);
     }
+    if (l.ff > 0 && l.ff_kind == HB_FF_MOE && l.shared_ff > 0) {
+      shape(2 * (size_t)l.shared_ff, W);
+      shape(W, l.shared_ff);
+    }
   }
   shape(m.sd.vocab, W);
   return f;
@@ -191,6 +195,8 @@ struct StackDims {
   int att_heads = 0, att_dim = 0;  // ... and their most heads / widest head (split workspace of the decode kernel)
   int att = 0;               // grouped-query layers the fused tcgen05 attention takes: widest heads * vdim
   int moe_e = 0, moe_f = 0;  // grouped tensor-core experts: most experts / widest expert over the layers that qualify
+  int vf = 0;                // layers that blend values: kv_heads * vdim
+  bool shared = false;       // some mixture has a unit every token uses
 };
 // Grouped-query layers whose prompt portions run on the fused tcgen05 attention kernel (the one the Llama path uses, with
 // the block mask and the unit of the denominator as parameters): bf16 mode, its head sizes, the pool's 64-position pages, and
@@ -198,7 +204,7 @@ struct StackDims {
 static bool gqa_fused_ok(const Model& m, const hb_layer_desc& l, int max_ctx) {
   static const bool off = [] { const char* e = getenv("HB_STACK_FUSED_ATTN"); return e && atoi(e) == 0; }();
   return !off && !m.sd.compute_f32 && l.mixer == HB_MIXER_GQA && l.dim == l.vdim && (l.dim == 64 || l.dim == 128) &&
-         (l.mask == HB_MASK_CHUNK || l.window >= max_ctx);
+         (l.mask == HB_MASK_CHUNK || l.window >= max_ctx) && !(l.attn_flags & HB_ATTN_LEARNED_SINK) && !(l.score_cap > 0.f);
 }
 // experts run as grouped tcgen05 products when the mode and the shapes allow (16-byte TMA strides, at least one MMA tile)
 static bool moe_grouped_ok(const Model& m, const hb_layer_desc& l) {
@@ -212,12 +218,22 @@ static StackDims stack_dims(const Model& m, int max_ctx) {
     const hb_layer_desc& l = m.sl[i];
     d.n1 = std::max(d.n1, std::max(m.sw[i].n_in, 2 * l.ff));
     d.mo = std::max(d.mo, std::max(l.heads * l.vdim, l.ff));
-    if (l.mixer == HB_MIXER_GLA) {
+    if (l.ff > 0 && l.ff_kind == HB_FF_MOE && l.shared_ff > 0) {
+      d.n1 = std::max(d.n1, 2 * l.shared_ff);
+      d.mo = std::max(d.mo, l.shared_ff);
+      d.gu = std::max(d.gu, 2 * l.shared_ff);
+      d.shared = true;
+    }
+    if (l.mixer == HB_MIXER_DELTA) {
+      d.n2 = std::max(d.n2, 2 * l.kv_heads * l.dim + l.heads * l.vdim + 2 * l.heads + l.kv_heads);
+      d.cx = std::max(d.cx, l.heads * l.vdim);
+    } else if (l.mixer == HB_MIXER_GLA) {
       d.n2 = std::max(d.n2, l.heads * l.dim);
       d.cx = std::max(d.cx, l.heads * l.vdim);
     } else if (l.mixer == HB_MIXER_GQA) {
       d.n2 = std::max(d.n2, l.heads * l.dim);
       d.rope_half += l.rope_dims / 2;
+      if (l.attn_flags & HB_ATTN_V_BLEND) d.vf = std::max(d.vf, l.kv_heads * l.vdim);
       if (gqa_fused_ok(m, l, max_ctx)) {
         d.att = std::max(d.att, l.heads * l.vdim);
         d.att_heads = std::max(d.att_heads, l.heads);
@@ -229,7 +245,7 @@ static StackDims stack_dims(const Model& m, int max_ctx) {
       d.qa = std::max(d.qa, l.heads * (l.kv_rank + l.rot_dim));
       d.cx = std::max(d.cx, std::max(l.heads * l.kv_rank, l.heads * l.vdim));
     }
-    if (l.ff > 0 && l.ff_kind == HB_FF_GELU_TANH) d.gu = std::max(d.gu, 2 * l.ff);
+    if (l.ff > 0 && (l.ff_kind == HB_FF_GELU_TANH || l.ff_kind == HB_FF_SILU)) d.gu = std::max(d.gu, 2 * l.ff);
     if (l.ff > 0 && l.ff_kind == HB_FF_MOE) {
       d.moe_r = std::max(d.moe_r, l.experts + l.identity_experts);
       d.moe_top = std::max(d.moe_top, l.top_k);
@@ -262,6 +278,9 @@ size_t Engine::workspace_bytes_stack() const {
     b += al256(std::max(T * (size_t)up8(dm.gu), rows * 2 * (size_t)dm.moe_f) * 2 + 256);
   }
   b += 2 * al256(T * W * 4) + al256(T * W * 2);                       // x, y, x16
+  if (sd.norm_place == HB_NORM_BOTH_SIDES) b += al256(T * W * 4);     // hn
+  if (dm.shared) b += al256(T * W * 4);                               // y2
+  if (dm.vf > 0) b += al256(T * (size_t)dm.vf * 4);                   // vfirst
   b += al256(T * (size_t)up8(n1) * 4) + al256(T * (size_t)up8(n2) * 4);  // p1, p2
   b += al256(T * (size_t)up8(q) * 4) + al256(T * (size_t)up8(q) * 2);     // cq, cq16
   b += al256(T * (size_t)up8(qa) * 4) + 2 * al256(T * (size_t)up8(cx) * 4);  // qabs, ctx (+ per-head value output)
@@ -285,6 +304,7 @@ int Engine::alloc_runtime_stack() {
   CU(stack_ops_init());
   CU(stack_gqa_init());
   CU(stack_moe_init());
+  CU(stack_delta_init());
   if (!sd.compute_f32) {  // stream-K plans allocate on first use of a shape: make them now, not inside a graph capture
     SmLimitScope sm_scope(cfg_.sm_budget);
     SkinnyPlan pl{};
@@ -296,6 +316,10 @@ int Engine::alloc_runtime_stack() {
       if (l.ff > 0) {
         CU(gemm_skinny_plan(2 * l.ff, sd.width, &pl));
         CU(gemm_skinny_plan(sd.width, l.ff, &pl));
+      }
+      if (l.ff > 0 && l.ff_kind == HB_FF_MOE && l.shared_ff > 0) {
+        CU(gemm_skinny_plan(2 * l.shared_ff, sd.width, &pl));
+        CU(gemm_skinny_plan(sd.width, l.shared_ff, &pl));
       }
     }
     CU(gemm_skinny_plan(sd.vocab, sd.width, &pl));
@@ -369,6 +393,9 @@ int Engine::alloc_runtime_stack() {
   sk_.x = (float*)take(T * W * 4);
   sk_.y = (float*)take(T * W * 4);
   sk_.x16 = (bf16*)take(T * W * 2);
+  sk_.hn = sd.norm_place == HB_NORM_BOTH_SIDES ? (float*)take(T * W * 4) : nullptr;
+  sk_.y2 = dm.shared ? (float*)take(T * W * 4) : nullptr;
+  sk_.vfirst = dm.vf > 0 ? (float*)take(T * (size_t)dm.vf * 4) : nullptr;
   sk_.p1 = (float*)take(T * (size_t)sk_.ld1 * 4);
   sk_.p2 = (float*)take(T * (size_t)sk_.ld2 * 4);
   sk_.cq = (float*)take(T * (size_t)sk_.ldcq * 4);
@@ -517,13 +544,55 @@ int Engine::forward_stack(int T, int B, const StepLayout& L, const int32_t* extr
   const double rowb = 4.0 * T * W;
 
   const float goff = sd.plain_gains ? 0.f : 1.f;  // stored norm gains are offsets from one unless plain
-  // the residual step: the norm covers the sum (post-norm stream) or the sublayer's output alone
-  auto resid = [&](const void* bias, const void* gain) -> cudaError_t {
+  const bool both = sd.norm_place == HB_NORM_BOTH_SIDES, tnorm = sd.norm_kind == HB_NORM_TANH;
+  // what a sublayer reads: the stream itself, or (norms on both sides) its normed copy; x16 is the bf16 copy of that
+  const float* xin = both ? k.hn : k.x;
+  // the residual step: the norm covers the sum (post-norm stream) or the sublayer's output alone; with norms on both sides
+  // the same launch also norms the input of the sublayer that follows (`pre`, null behind the last one)
+  auto resid = [&](const void* bias, const void* gain, const void* pre) -> cudaError_t {
+    if (tnorm) {
+      cudaError_t e = tanh_norm_step(stream_, k.x, nullptr, k.y, W, gain, both ? pre : nullptr, f32, k.x, both && pre ? k.hn : nullptr,
+                                     both && pre ? x16 : nullptr, T, W);
+      if (e == cudaSuccess && !both && x16) e = to_bf16_rows(stream_, k.x, W, x16, W, T, W);
+      return e;
+    }
+    if (both) {
+      cudaError_t e = resid_add_normed(stream_, k.x, nullptr, k.y, W, bias, gain, f32, goff, sd.norm_eps, T, W);
+      if (e == cudaSuccess && pre) e = norm_rows_f32(stream_, k.x, nullptr, pre, f32, goff, sd.norm_eps, k.hn, x16, T, W);
+      return e;
+    }
     if (sd.norm_place == HB_NORM_OF_OUTPUT) return resid_add_normed(stream_, k.x, x16, k.y, W, bias, gain, f32, goff, sd.norm_eps, T, W);
     return resid_postnorm(stream_, k.x, x16, k.y, W, bias, gain, f32, sd.resid_alpha, goff, sd.norm_eps, T, W);
   };
-  SPAN(3, rowb, embed_rows_f32(stream_, tokens, model_.s_embed, f32, k.x, x16, T, W));
-  if (sd.embed_norm) SPAN(3, 2 * rowb, norm_rows_f32(stream_, k.x, nullptr, model_.s_embed_norm, f32, goff, sd.norm_eps, k.x, x16, T, W));
+  // a row norm outside the residual step (embedding, first sublayer's input, final norm)
+  auto norm_rows = [&](const float* src, const int32_t* idx, const void* nw, float* out, bf16* out16, int rows) -> cudaError_t {
+    if (tnorm) return tanh_norm_step(stream_, src, idx, nullptr, 0, nullptr, nw, f32, nullptr, out, out16, rows, W);
+    return norm_rows_f32(stream_, src, idx, nw, f32, goff, sd.norm_eps, out, out16, rows, W);
+  };
+  // gated unit y = down(act(gate) * up) of inner size F from the sublayer's input (dense feed-forwards, the unit every token
+  // of a mixture uses).  Steps of many tokens: both products on the tcgen05 GEMM, the gated pair applied on the accumulators'
+  // way out (packed [128 gate | 128 up] weight tiles) or on the bf16 [gate | up] rows between them.
+  auto gated_ff = [&](const void* w_gu, const void* w_down, int F, int act, float limit, bool packed, float* out) -> int {
+    int rc;
+    if (T > 256 && k.gu16 && F % 8 == 0 && stack_tc(2 * F, W, W, W) && stack_tc(W, F, F, W)) {
+      if (packed && act != GLU_CLAMPED) {
+        GemmArgs g{x16, W, (const bf16*)w_gu, W, mo16, F, nullptr, 0, nullptr, T, 2 * F, W, act == GLU_GELU_TANH ? EPI_GEGLU : EPI_SWIGLU, 0};
+        SPAN(0, 4.0 * T * F * W, gemm_bf16_tn(stream_, g));
+      } else {
+        GemmArgs g{x16, W, (const bf16*)w_gu, W, k.gu16, 2 * F, nullptr, 0, nullptr, T, 2 * F, W, EPI_NONE, 0};
+        SPAN(0, 4.0 * T * F * W, gemm_bf16_tn(stream_, g));
+        SPAN(3, 6.0 * T * F, gated_unit_b16(stream_, k.gu16, 2 * F, act, mo16, T, F, limit));
+      }
+    } else {
+      rc = stack_gemm(xin, x16, W, w_gu, 2 * F, W, k.p1, k.ld1, T);
+      if (rc != HB_OK) return rc;
+      SPAN(3, 12.0 * T * F, gated_unit(stream_, k.p1, k.ld1, act, k.mo, mo16, T, F, packed, limit));
+    }
+    return stack_gemm(k.mo, mo16, F, w_down, W, F, out, W, T);
+  };
+  SPAN(3, rowb, embed_rows_f32(stream_, tokens, model_.s_embed, f32, k.x, x16, T, W, sd.embed_scale != 0.f ? sd.embed_scale : 1.f));
+  if (sd.embed_norm) SPAN(3, 2 * rowb, norm_rows(k.x, nullptr, model_.s_embed_norm, k.x, both ? nullptr : x16, T));
+  if (both) SPAN(3, 2 * rowb, norm_rows(k.x, nullptr, model_.sw[0].norm1, k.hn, x16, T));
   for (size_t si = 0; si < k.freq_sets.size(); ++si)  // cos / sin of the step's positions, once per distinct rotation
     SPAN(3, 8.0 * T * k.freq_half[si], stack_rope_table(stream_, positions, k.freq_sets[si], k.freq_half[si], k.rope_cs[si], T));
   for (int i = 0; i < sd.n_layers; ++i) {
@@ -533,9 +602,31 @@ int Engine::forward_stack(int T, int B, const StepLayout& L, const int32_t* extr
     // every projection that reads the stream, in one GEMM
     // (grouped-query layers keep the rows of this product dense: the buffer's stride is sized for the widest gated unit)
     const int ldin = l.mixer == HB_MIXER_GQA ? up8(w.n_in) : k.ld1;
-    int rc = stack_gemm(k.x, x16, W, w.w_in, w.n_in, W, k.p1, ldin, T);
+    int rc = stack_gemm(xin, x16, W, w.w_in, w.n_in, W, k.p1, ldin, T);
     if (rc != HB_OK) return rc;
-    if (l.mixer == HB_MIXER_GLA) {
+    // the norm that prepares the input of whatever follows a sublayer (norms on both sides)
+    const void* pre_next = i + 1 < sd.n_layers ? model_.sw[i + 1].norm1 : nullptr;
+    if (l.mixer == HB_MIXER_DELTA) {
+      const int G = l.kv_heads, GD = G * Dk, C = 2 * GD + H * Dv;
+      DeltaPrepArgs pa{};
+      pa.p = k.p1; pa.ldp = k.ld1; pa.off_qkv = w.off_q; pa.off_b = w.off_b; pa.off_a = w.off_a;
+      pa.conv_w = w.conv_w; pa.a_dt = w.a_dt; pa.f32 = f32; pa.taps = l.conv_taps;
+      pa.out = k.p2; pa.ldo = k.ld2;
+      pa.state = state_; pa.slot_stride = (long)model_.state_floats; pa.tail_off = w.tail_off;
+      pa.cu = cu; pa.first_pos = first; pa.slots = sslot; pa.seq_of = seqof;
+      pa.T = T; pa.B = B; pa.H = H; pa.G = G; pa.D = Dk; pa.Dv = Dv;
+      SPAN(3, 8.0 * T * C * (l.conv_taps + 1), delta_prep(stream_, pa));
+      SPAN(3, 8.0 * B * C * l.conv_taps, delta_conv_tails(stream_, pa));
+      DeltaArgs da{};
+      da.in = k.p2; da.ld = k.ld2;
+      da.off_q = 0; da.off_k = GD; da.off_v = 2 * GD; da.off_beta = C; da.off_decay = C + H; da.off_kq = C + 2 * H;
+      da.out = k.ctx; da.ldo = k.ldctx;
+      da.state = state_ + w.state_off; da.slot_stride = (long)model_.state_floats;
+      da.cu = cu; da.first_pos = first; da.slots = sslot;
+      da.B = B; da.H = H; da.G = G; da.D = Dk; da.Dv = Dv;
+      SPAN(6, 6.0 * T * H * Dk * Dv, delta_recurrence(stream_, da));
+      SPAN(3, 12.0 * T * H * Dv, headnorm_silu_gate(stream_, k.ctx, k.ldctx, k.p1 + w.off_g, k.ld1, w.hnorm, f32, sd.norm_eps, k.mo, mo16, T, H, Dv));
+    } else if (l.mixer == HB_MIXER_GLA) {
       // decay: z = a2 (a1 x) + b -> sigmoid(z)^(1/tau), fp32
       rc = stack_gemm(k.p1 + w.off_a1, nullptr, k.ld1, w.a2, H * Dk, l.decay_rank, k.p2, k.ld2, T);
       if (rc != HB_OK) return rc;
@@ -574,6 +665,9 @@ int Engine::forward_stack(int T, int B, const StepLayout& L, const int32_t* extr
       pa.cs = k.layer_set[i] >= 0 ? k.rope_cs[k.layer_set[i]] : nullptr; pa.rope_dims = l.rope_dims; pa.pairing = l.rope_pairing;
       pa.H = H; pa.G = G; pa.D = Dk; pa.Dv = Dv; pa.page_size = page_;
       pa.unit_norm = (l.attn_flags & HB_ATTN_QK_UNIT_NORM) != 0; pa.eps = sd.norm_eps; pa.T = T;
+      pa.bias = (l.attn_flags & HB_ATTN_QKV_BIAS) ? w.b_in : nullptr;
+      pa.proj_norm = (l.attn_flags & HB_ATTN_QK_PROJ_NORM) != 0; pa.qk_gain = w.qk_gain;
+      pa.blend_role = w.blend_role; pa.vmix = w.vmix; pa.v_first = k.vfirst;
       SPAN(3, 8.0 * T * (H + 2 * G) * Dk, gqa_prep(stream_, pa));
       if (tc_dec) {
         AttnDecodeArgs da{};
@@ -620,6 +714,7 @@ int Engine::forward_stack(int T, int B, const StepLayout& L, const int32_t* extr
       aa.out = k.mo; aa.ldo = H * Dv; aa.out_b16 = mo16;
       aa.T = T; aa.H = H; aa.G = G; aa.D = Dk; aa.Dv = Dv; aa.mask = l.mask; aa.window = l.window;
       aa.unit_sink = (l.attn_flags & HB_ATTN_UNIT_SINK) != 0; aa.scale = l.scale;
+      aa.softcap = l.score_cap; aa.sink = (l.attn_flags & HB_ATTN_LEARNED_SINK) ? w.sink : nullptr;
       SPAN(7, 2.0 * T * H * (double)std::min(l.window, cfg_.max_ctx) * (Dk + Dv), gqa_attn(stream_, aa));
       }
     } else {
@@ -717,23 +812,33 @@ int Engine::forward_stack(int T, int B, const StepLayout& L, const int32_t* extr
     }
     rc = stack_gemm(k.mo, mo16, H * Dv, w.wo, W, H * Dv, k.y, W, T);
     if (rc != HB_OK) return rc;
-    SPAN(3, 3 * rowb, resid(nullptr, w.norm1));
+    SPAN(3, 3 * rowb, resid(nullptr, both ? w.norm1b : w.norm1, l.ff > 0 ? w.norm2 : pre_next));
     if (l.ff > 0 && l.ff_kind == HB_FF_MOE) {
       // router in fp32 on the stream itself; experts per (token, choice); identity outputs and weights in the combination
       const int E = l.experts, R = l.experts + l.identity_experts, F = l.ff;
+      RouteOpts ro;
+      ro.sigmoid = l.router_kind == HB_ROUTER_SIGMOID; ro.groups = l.route_groups; ro.keep = l.route_keep; ro.renorm = l.route_renorm;
+      ro.scale = l.route_scale != 0.f ? l.route_scale : 1.f;
+      const int eact = l.expert_kind == HB_EXPERT_CLAMPED ? GLU_CLAMPED : GLU_SILU;
+      const float* add = nullptr;
+      if (l.shared_ff > 0) {  // the unit every token uses; the combination below starts from its output
+        rc = gated_ff(w.w_gu_sh, w.w_down_sh, l.shared_ff, eact, l.shared_limit, false, k.y2);
+        if (rc != HB_OK) return rc;
+        add = k.y2;
+      }
       if (T > 256 && R <= 64 && stack_tc(64, W, W, k.ldz) && k.ldz >= 64) {
         // steps of many tokens: logits on the tensor cores from the bf16 copy of the stream (fp32 accumulation; the router's
         // rows are padded with zero rows to one MMA tile), then the choice in fp32
         GemmArgs g{x16, W, (const bf16*)w.router, W, k.moe_z, k.ldz, nullptr, 0, nullptr, T, 64, W, EPI_F32, 0};
         SPAN(0, 2.0 * T * 64 * W, gemm_bf16_tn(stream_, g));
-        SPAN(3, 8.0 * T * R, moe_route(stream_, k.moe_z, k.ldz, w.correction, f32, R, l.top_k, k.moe_ids, k.moe_w, T));
+        SPAN(3, 8.0 * T * R, moe_route(stream_, k.moe_z, k.ldz, w.correction, f32, R, l.top_k, k.moe_ids, k.moe_w, T, ro));
       } else if (moe_router_smem(R, W, f32) <= 200 * 1024) {
-        SPAN(3, 4.0 * T * W, moe_router(stream_, k.x, w.router, w.correction, f32, R, W, l.top_k, k.moe_ids, k.moe_w, T,
-                                        cfg_.sm_budget > 0 ? cfg_.sm_budget : 148));
+        SPAN(3, 4.0 * T * W, moe_router(stream_, xin, w.router, w.correction, f32, R, W, l.top_k, k.moe_ids, k.moe_w, T,
+                                        cfg_.sm_budget > 0 ? cfg_.sm_budget : 148, ro));
       } else {  // a router too large for shared memory: product, then choice
-        GemmRtArgs g{k.x, W, 0, w.router, W, 1, 0, k.moe_z, k.ldz, 0, nullptr, T, R, W, 1, f32};
+        GemmRtArgs g{xin, W, 0, w.router, W, 1, 0, k.moe_z, k.ldz, 0, nullptr, T, R, W, 1, f32};
         SPAN(5, 2.0 * T * R * W, gemm_rt(stream_, g));
-        SPAN(3, 8.0 * T * R, moe_route(stream_, k.moe_z, k.ldz, w.correction, f32, R, l.top_k, k.moe_ids, k.moe_w, T));
+        SPAN(3, 8.0 * T * R, moe_route(stream_, k.moe_z, k.ldz, w.correction, f32, R, l.top_k, k.moe_ids, k.moe_w, T, ro));
       }
       const int items = T * l.top_k;
       if (moe_grouped_ok(model_, l) && k.moe_a16 && items >= 2 * E) {
@@ -750,46 +855,31 @@ int Engine::forward_stack(int T, int B, const StepLayout& L, const int32_t* extr
           GemmArgs g1{k.moe_a16, W, (const bf16*)w.w_gu, W, k.gu16, 2 * F, nullptr, 0, nullptr, rows, 2 * F, W, EPI_NONE, 0};
           g1.m_tile_group = k.moe_tiles; g1.groups = E;
           SPAN(0, 4.0 * rows * F * W, gemm_bf16_tn(stream_, g1));
-          SPAN(3, 6.0 * rows * F, gated_unit_b16(stream_, k.gu16, 2 * F, GLU_SILU, k.moe_h16, rows, F));
+          SPAN(3, 6.0 * rows * F, gated_unit_b16(stream_, k.gu16, 2 * F, eact, k.moe_h16, rows, F, l.ff_limit));
         }
         GemmArgs g2{k.moe_h16, F, (const bf16*)w.w_down, F, k.moe_y16, W, nullptr, 0, nullptr, rows, W, F, EPI_NONE, 0};
         g2.m_tile_group = k.moe_tiles; g2.groups = E;
         SPAN(0, 2.0 * rows * F * W, gemm_bf16_tn(stream_, g2));
-        SPAN(3, 2.0 * T * (l.top_k + 4) * W, moe_combine_rows(stream_, k.x, k.moe_y16, k.moe_row_of, k.moe_w, l.top_k, k.y, T, W));
+        SPAN(3, 2.0 * T * (l.top_k + 4) * W, moe_combine_rows(stream_, xin, k.moe_y16, k.moe_row_of, k.moe_w, l.top_k, k.y, T, W, add));
       } else {
-        SPAN(5, 6.0 * items * F * W, moe_expert_rows(stream_, k.x, x16, w.w_gu, w.w_down, f32, k.moe_ids, l.top_k, E, F, W, k.moe_y, T, w.gu_packed));
-        SPAN(3, 4.0 * T * (l.top_k + 2) * W, moe_combine(stream_, k.x, k.moe_y, k.moe_ids, k.moe_w, l.top_k, E, k.y, T, W));
+        SPAN(5, 6.0 * items * F * W, moe_expert_rows(stream_, xin, x16, w.w_gu, w.w_down, f32, k.moe_ids, l.top_k, E, F, W, k.moe_y, T, w.gu_packed,
+                                                     eact, l.ff_limit));
+        SPAN(3, 4.0 * T * (l.top_k + 2) * W, moe_combine(stream_, xin, k.moe_y, k.moe_ids, k.moe_w, l.top_k, E, k.y, T, W, add));
       }
-      SPAN(3, 3 * rowb, resid(nullptr, w.norm2));
-    } else if (l.ff > 0 && l.ff_kind == HB_FF_GELU_TANH) {
-      const int F = l.ff;
-      if (T > 256 && k.gu16 && F % 8 == 0 && stack_tc(2 * F, W, W, W) && stack_tc(W, F, F, W)) {
-        // steps of many tokens: both products on the tcgen05 GEMM, the [gate | up] rows travel between them as bf16
-        if (w.gu_packed) {  // gelu_tanh(gate) * up on the accumulators' way out
-          GemmArgs g{x16, W, (const bf16*)w.w_gu, W, mo16, F, nullptr, 0, nullptr, T, 2 * F, W, EPI_GEGLU, 0};
-          SPAN(0, 4.0 * T * F * W, gemm_bf16_tn(stream_, g));
-        } else {
-          GemmArgs g{x16, W, (const bf16*)w.w_gu, W, k.gu16, 2 * F, nullptr, 0, nullptr, T, 2 * F, W, EPI_NONE, 0};
-          SPAN(0, 4.0 * T * F * W, gemm_bf16_tn(stream_, g));
-          SPAN(3, 6.0 * T * F, gated_unit_b16(stream_, k.gu16, 2 * F, GLU_GELU_TANH, mo16, T, F));
-        }
-      } else {
-        rc = stack_gemm(k.x, x16, W, w.w_gu, 2 * F, W, k.p1, k.ld1, T);
-        if (rc != HB_OK) return rc;
-        SPAN(3, 12.0 * T * F, gated_unit(stream_, k.p1, k.ld1, GLU_GELU_TANH, k.mo, mo16, T, F, w.gu_packed));
-      }
-      rc = stack_gemm(k.mo, mo16, F, w.w_down, W, F, k.y, W, T);
+      SPAN(3, 3 * rowb, resid(nullptr, both ? w.norm2b : w.norm2, pre_next));
+    } else if (l.ff > 0 && (l.ff_kind == HB_FF_GELU_TANH || l.ff_kind == HB_FF_SILU)) {
+      rc = gated_ff(w.w_gu, w.w_down, l.ff, l.ff_kind == HB_FF_SILU ? GLU_SILU : GLU_GELU_TANH, 0.f, w.gu_packed, k.y);
       if (rc != HB_OK) return rc;
-      SPAN(3, 3 * rowb, resid(nullptr, w.norm2));
+      SPAN(3, 3 * rowb, resid(nullptr, both ? w.norm2b : w.norm2, pre_next));
     } else if (l.ff > 0) {
       const int F = l.ff;
-      rc = stack_gemm(k.x, x16, W, w.w_gu, 2 * F, W, k.p1, k.ld1, T);
+      rc = stack_gemm(xin, x16, W, w.w_gu, 2 * F, W, k.p1, k.ld1, T);
       if (rc != HB_OK) return rc;
       const void* bu = (const uint8_t*)w.b_gu + (size_t)F * model_.elem;
       SPAN(3, 12.0 * T * F, clamped_glu(stream_, k.p1, k.ld1, w.b_gu, bu, f32, l.ff_limit, 1.702f, k.mo, mo16, T, F));
       rc = stack_gemm(k.mo, mo16, F, w.w_down, W, F, k.y, W, T);
       if (rc != HB_OK) return rc;
-      SPAN(3, 3 * rowb, resid(w.b_down, w.norm2));
+      SPAN(3, 3 * rowb, resid(w.b_down, both ? w.norm2b : w.norm2, pre_next));
     }
   }
   // logits: final norm -> head -> soft cap, for the entries' last rows (sampling) and for the rows asked for
@@ -798,11 +888,11 @@ int Engine::forward_stack(int T, int B, const StepLayout& L, const int32_t* extr
       const int m = std::min(t_cap_, n - r0);
       const int32_t* idx = rows ? rows + r0 : nullptr;
       const float* src = rows ? k.x : k.x + (size_t)r0 * W;
-      LAUNCH(norm_rows_f32(stream_, src, idx, model_.s_final_norm, f32, goff, sd.norm_eps, k.y, x16, m, W));
+      LAUNCH(norm_rows(src, idx, model_.s_final_norm, k.y, x16, m));
       int rc = stack_gemm(k.y, x16, W, model_.s_head, V, W, out + (size_t)r0 * V, V, m);
       if (rc != HB_OK) return rc;
     }
-    LAUNCH(softcap_rows(stream_, out, (size_t)n * V, sd.logit_softcap));
+    LAUNCH(softcap_rows(stream_, out, (size_t)n * V, sd.logit_softcap, sd.logit_scale != 0.f ? sd.logit_scale : 1.f));
     return HB_OK;
   };
   if (n_extra > 0) {

@@ -271,8 +271,14 @@ struct GemmRtArgs {
 };
 cudaError_t gemm_rt(cudaStream_t s, const GemmRtArgs& a);
 
-// x[t, :] = table[tokens[t], :] as fp32 (+ bf16 copy)
-cudaError_t embed_rows_f32(cudaStream_t s, const int32_t* tokens, const void* table, bool f32, float* x, bf16* x_b16, int T, int W);
+// x[t, :] = table[tokens[t], :] * scale as fp32 (+ bf16 copy)
+cudaError_t embed_rows_f32(cudaStream_t s, const int32_t* tokens, const void* table, bool f32, float* x, bf16* x_b16, int T, int W,
+                           float scale = 1.f);
+// Residual step between element-wise norms N(v) = tanh(alpha v) * w + b; `post` / `pre` are blocks [w (W) | b (W) | alpha] of
+// the weight type or null.  v = x[row_index ? row_index[r] : r]; with y: v += post ? N_post(y[r]) : y[r] and x_out[r] = v
+// (x_out may be x); with pre: h[r] = N_pre(v) as fp32 (h) and / or bf16 (h_b16).
+cudaError_t tanh_norm_step(cudaStream_t s, const float* x, const int32_t* row_index, const float* y, long ldy, const void* post,
+                           const void* pre, bool f32, float* x_out, float* h, bf16* h_b16, int rows, int W);
 // Post-norm residual step: x[t] <- rmsnorm(alpha * x[t] + y[t] (+ bias)) * (gain_offset + w);  rows of y have stride ldy
 cudaError_t resid_postnorm(cudaStream_t s, float* x, bf16* x_b16, const float* y, long ldy, const void* bias, const void* w,
                            bool f32, float alpha, float gain_offset, float eps, int T, int W);
@@ -282,8 +288,8 @@ cudaError_t resid_add_normed(cudaStream_t s, float* x, bf16* x_b16, const float*
 // out[r] = rmsnorm(x[row_index ? row_index[r] : r]) * (gain_offset + w)   (out may be x itself when row_index is null)
 cudaError_t norm_rows_f32(cudaStream_t s, const float* x, const int32_t* row_index, const void* w, bool f32, float gain_offset,
                           float eps, float* out, bf16* out_b16, int rows, int W);
-// logits <- cap * tanh(logits / cap), in place on [rows, V]
-cudaError_t softcap_rows(cudaStream_t s, float* logits, size_t n, float cap);
+// logits <- scale * logits, then cap * tanh(logits / cap) when cap > 0; in place on [rows, V]
+cudaError_t softcap_rows(cudaStream_t s, float* logits, size_t n, float cap, float scale = 1.f);
 // Clamped gated unit: g = min(G + bg, limit); u = clamp(U + bu, -limit, limit); out = g * sigmoid(act_alpha * g) * (u + 1)
 // with G = gu[t, j], U = gu[t, F + j] (row stride ldg)
 cudaError_t clamped_glu(cudaStream_t s, const float* gu, long ldg, const void* bias_g, const void* bias_u, bool f32, float limit,
@@ -375,6 +381,13 @@ struct GqaPrepArgs {
   int H, G, D, Dv, page_size;
   bool unit_norm; float eps;
   int T;
+  // Options served by one block per token (any of them set): bias [q | k | v columns of p] of the cache element type added
+  // first; proj_norm: q (and k) divided by the root mean square over ALL their heads' entries and multiplied by
+  // qk_gain [H*D | G*D] (instead of unit_norm per head); blend_role 1: the (biased) values also go to v_first[t][G*Dv];
+  // 2: values become (1 - l) v + l v_first[t], l = vmix[0], before they are cached.
+  const void* bias = nullptr;
+  bool proj_norm = false; const void* qk_gain = nullptr;
+  int blend_role = 0; const void* vmix = nullptr; float* v_first = nullptr;
 };
 cudaError_t gqa_prep(cudaStream_t s, const GqaPrepArgs& a);
 // cs[t][2i] = cos(a), cs[t][2i+1] = sin(a), a = positions[t] * freqs[i], i < half: the angle and its reduction to one turn in
@@ -394,6 +407,8 @@ struct GqaAttnArgs {
   float* out; long ldo; bf16* out_b16;
   int T, H, G, D, Dv, mask, window;
   bool unit_sink; float scale;
+  float softcap = 0.f;         // > 0: s <- softcap * tanh(s / softcap) after the scale
+  const void* sink = nullptr;  // [H] of the cache element type: exp(sink_h) joins the denominator (instead of unit_sink)
 };
 cudaError_t gqa_attn(cudaStream_t s, const GqaAttnArgs& a);
 size_t gqa_attn_smem(int D, int Dv, int max_keys);  // dynamic shared memory the kernel needs to see max_keys keys
@@ -401,29 +416,70 @@ size_t gqa_attn_smem(int D, int Dv, int max_keys);  // dynamic shared memory the
 cudaError_t head_gate_rows(cudaStream_t s, const bf16* o, long ldo, const float* gate, long ldg, float* out, bf16* out_b16, int T, int H,
                            int Dv);
 
+// ---- gated delta rule (stack_delta.cu).  Step entries as for gla_recurrence; a state slot holds, per layer, S [H][D][Dv] and
+//      the last taps - 1 inputs of the convolutions [taps - 1][2 G D + H Dv] (at float offset tail_off of the slot).
+cudaError_t stack_delta_init();
+// From the fused projection p[t] = [.. q (G*D) | k (G*D) | v (H*Dv) at off_qkv .. | b (H) at off_b | a (H) at off_a]:
+// causal convolution over `taps` tokens per channel (conv_w [channels][taps], last tap = the token itself; inputs before the
+// entry come from the slot, zeros before position 0), silu; q and k to unit vectors per head (q also times D^-1/2);
+// out[t] = [q | k | v | beta = sigmoid(b) (H) | decay = exp(-exp(A_log) softplus(a + dt_bias)) (H) | k . q (G)]
+struct DeltaPrepArgs {
+  const float* p; long ldp; int off_qkv, off_b, off_a;
+  const void* conv_w; const void* a_dt; bool f32;   // a_dt = [A_log (H) | dt_bias (H)]
+  int taps;
+  float* out; long ldo;
+  float* state; long slot_stride; size_t tail_off;
+  const int32_t* cu; const int32_t* first_pos; const int32_t* slots; const int32_t* seq_of;
+  int T, B, H, G, D, Dv;
+};
+cudaError_t delta_prep(cudaStream_t s, const DeltaPrepArgs& a);
+// after delta_prep of the same step: the slots' convolution inputs advance by the entries' tokens
+cudaError_t delta_conv_tails(cudaStream_t s, const DeltaPrepArgs& a);
+// S <- g S; u = beta (v - S^T k); S <- S + k u^T; o = S^T q per (entry, head); query / key head of head h: h / (H / G)
+struct DeltaArgs {
+  const float* in; long ld;                       // delta_prep's rows
+  int off_q, off_k, off_v, off_beta, off_decay, off_kq;
+  float* out; long ldo;                           // [T, H*Dv]
+  float* state; long slot_stride;                 // state + slot * slot_stride -> this layer's [H][D][Dv]
+  const int32_t* cu; const int32_t* first_pos; const int32_t* slots;
+  int B, H, G, D, Dv;
+};
+cudaError_t delta_recurrence(cudaStream_t s, const DeltaArgs& a);
+
 // ---- gated feed-forward units and mixtures of experts (stack_moe.cu).
 cudaError_t stack_moe_init();
-enum GluAct : int { GLU_SILU = 0, GLU_GELU_TANH = 1 };
+enum GluAct : int { GLU_SILU = 0, GLU_GELU_TANH = 1, GLU_CLAMPED = 2 };
+// GLU_CLAMPED: g = min(gate, limit), u = clamp(up, -limit, limit), g * sigmoid(1.702 g) * (u + 1); the others act(gate) * up.
+// How a router turns logits into a choice.  softmax or sigmoid scores; the top_k largest of (score + correction) among the
+// eligible outputs are chosen, lowest index first among equals: with groups > 1 the outputs form that many equal groups of
+// neighbours, a group scores the sum of its two largest corrected scores and only the `keep` best groups are eligible.
+// The weights are the chosen outputs' uncorrected scores, divided by their sum (+ 1e-20) when renorm, times scale.
+struct RouteOpts {
+  int sigmoid = 0, groups = 0, keep = 0, renorm = 0;
+  float scale = 1.f;
+};
 // out[t, j] = act(gu[t, j]) * gu[t, F + j]   (row stride ldg; out may be null when only the bf16 copy is wanted)
 // packed: the columns come from weights stored per 256-row tile as [128 gate | 128 up] (the layout of EPI_SWIGLU / EPI_GEGLU):
 // gate j of tile i at column 256 i + j, its up at 256 i + 128 + j, output column 128 i + j (F a multiple of 128)
-cudaError_t gated_unit(cudaStream_t s, const float* gu, long ldg, int act, float* out, bf16* out_b16, int T, int F, bool packed = false);
+cudaError_t gated_unit(cudaStream_t s, const float* gu, long ldg, int act, float* out, bf16* out_b16, int T, int F, bool packed = false,
+                       float limit = 0.f);
 // Router: scores = softmax(z[t, :R]) in fp32; the top_k largest of (score + correction) are chosen, lowest index first among
 // equals; ids[t, k] = chosen output, wts[t, k] = its score (not renormalised)
 cudaError_t moe_route(cudaStream_t s, const float* z, long ldz, const void* correction, bool f32, int R, int top_k, int32_t* ids,
-                      float* wts, int T);
+                      float* wts, int T, const RouteOpts& ro = RouteOpts());
 // moe_route fused with the router's product: z = router x[t] in fp32 (router [R][W] of the weight type, held in shared
 // memory: moe_router_smem(R, W, f32) <= 200 KB, else use gemm_rt + moe_route), then the same choice.  sms: blocks to launch
 size_t moe_router_smem(int R, int W, bool f32);
 cudaError_t moe_router(cudaStream_t s, const float* x, const void* router, const void* correction, bool f32, int R, int W, int top_k,
-                       int32_t* ids, float* wts, int T, int sms);
+                       int32_t* ids, float* wts, int T, int sms, const RouteOpts& ro = RouteOpts());
 // bf16 form of gated_unit for the tensor-core path: gu and out are bf16, F and ldg multiples of eight
-cudaError_t gated_unit_b16(cudaStream_t s, const bf16* gu, long ldg, int act, bf16* out, int T, int F);
+cudaError_t gated_unit_b16(cudaStream_t s, const bf16* gu, long ldg, int act, bf16* out, int T, int F, float limit = 0.f);
 // One block per (token, choice): y[(t, k), :] = down_e(silu(gate_e x_t) * (up_e x_t)) for ids[t, k] = e < E (rows of choices
 // that name an identity output are left alone).  x_b16 != null: the unit reads the bf16 copy of x and rounds its inner
 // activation to bf16, as the tensor-core path does.  w_gu: [E][2F][W] ([gate | up] rows), w_down: [E][W][F].
 cudaError_t moe_expert_rows(cudaStream_t s, const float* x, const bf16* x_b16, const void* w_gu, const void* w_down, bool f32,
-                            const int32_t* ids, int top_k, int E, int F, int W, float* y, int T, bool packed = false);
+                            const int32_t* ids, int top_k, int E, int F, int W, float* y, int T, bool packed = false, int act = GLU_SILU,
+                            float limit = 0.f);
 // The same experts as grouped tensor-core products (bf16 mode): moe_group_rows sorts the (token, choice) items by expert into
 // a row buffer of moe_group_max_rows(items, E) rows whose per-expert segments start on multiples of 128 rows (row_of[item] =
 // its row or -1 for an identity output, src_of_row[row] = its token or -1, tile_group[row / 128] = the expert whose weights
@@ -434,9 +490,9 @@ cudaError_t moe_group_rows(cudaStream_t s, const int32_t* ids, int n_items, int 
                            int32_t* tile_group, int32_t* scratch);  // scratch: 3 E ints
 cudaError_t moe_gather_rows(cudaStream_t s, const bf16* x16, int W, const int32_t* src_of_row, bf16* a16, int rows);
 cudaError_t moe_combine_rows(cudaStream_t s, const float* x, const bf16* y, const int32_t* row_of, const float* wts, int top_k,
-                             float* out, int T, int W);
-// out[t, :] = sum_k wts[t, k] * (ids[t, k] < E ? y[(t, k), :] : x[t, :]), k in order
+                             float* out, int T, int W, const float* add = nullptr);
+// out[t, :] = (add ? add[t, :] : 0) + sum_k wts[t, k] * (ids[t, k] < E ? y[(t, k), :] : x[t, :]), k in order (add may be out)
 cudaError_t moe_combine(cudaStream_t s, const float* x, const float* y, const int32_t* ids, const float* wts, int top_k, int E,
-                        float* out, int T, int W);
+                        float* out, int T, int W, const float* add = nullptr);
 
 }  // namespace hb

@@ -197,6 +197,18 @@ std::string validate_stack(const hb_stack_desc& d, const hb_layer_desc* L) {
       if (l.mask != HB_MASK_CAUSAL && l.window <= 0) return "window / chunk size must be positive" + at;
       if (l.dim > 512 || l.vdim > 512) return "head size > 512 unsupported" + at;
       if (l.kv_from >= 0) return "kv_from is a latent-attention option" + at;
+      if ((l.attn_flags & HB_ATTN_QK_PROJ_NORM) && (l.attn_flags & HB_ATTN_QK_UNIT_NORM)) return "two q / k norms" + at;
+      if ((l.attn_flags & HB_ATTN_LEARNED_SINK) && (l.attn_flags & HB_ATTN_UNIT_SINK)) return "two softmax sinks" + at;
+      if ((l.attn_flags & HB_ATTN_V_BLEND) && (l.attn_flags & HB_ATTN_V_IS_K)) return "blended values need a value projection" + at;
+      if (l.attn_flags & HB_ATTN_V_BLEND)
+        for (int j = 0; j < i; ++j)
+          if (L[j].mixer == HB_MIXER_GQA && (L[j].attn_flags & HB_ATTN_V_BLEND) && L[j].kv_heads * L[j].vdim != l.kv_heads * l.vdim)
+            return "layers that blend values need equal kv_heads * vdim" + at;
+      if ((size_t)(l.heads + l.kv_heads) * l.dim + (size_t)l.kv_heads * l.vdim > 24 * 1024) return "q + k + v row > 24576 entries unsupported" + at;
+    } else if (l.mixer == HB_MIXER_DELTA) {
+      if (l.kv_heads <= 0 || l.heads % l.kv_heads) return "heads must be a multiple of kv_heads" + at;
+      if (l.dim > 256) return "delta-rule key channels per head > 256 unsupported" + at;
+      if (l.conv_taps < 1 || l.conv_taps > 16) return "convolution taps must be 1..16" + at;
     } else {
       return "unknown mixer" + at;
     }
@@ -205,12 +217,27 @@ std::string validate_stack(const hb_stack_desc& d, const hb_layer_desc* L) {
       if (l.ff_kind == HB_FF_MOE) {
         if (l.experts <= 0 || l.identity_experts < 0 || l.top_k <= 0 || l.top_k > l.experts + l.identity_experts) return "mixture-of-experts sizes" + at;
         if (l.experts + l.identity_experts > 1024 || l.top_k > 32) return "more than 1024 router outputs or top_k > 32 unsupported" + at;
-      } else if (l.ff_kind != HB_FF_CLAMPED && l.ff_kind != HB_FF_GELU_TANH) {
+        if (l.router_kind != HB_ROUTER_SOFTMAX && l.router_kind != HB_ROUTER_SIGMOID) return "unknown router kind" + at;
+        if (l.expert_kind != HB_EXPERT_SILU && l.expert_kind != HB_EXPERT_CLAMPED) return "unknown expert kind" + at;
+        if (l.route_groups > 1) {
+          const int R = l.experts + l.identity_experts;
+          if (R % l.route_groups) return "router outputs must divide into the groups" + at;
+          if (l.route_keep <= 0 || l.route_keep > l.route_groups) return "groups kept must be 1..groups" + at;
+          if (l.route_keep * (R / l.route_groups) < l.top_k) return "the kept groups hold fewer outputs than top_k" + at;
+        }
+        if (l.shared_ff < 0) return "negative shared_ff" + at;
+      } else if (l.ff_kind != HB_FF_CLAMPED && l.ff_kind != HB_FF_GELU_TANH && l.ff_kind != HB_FF_SILU) {
         return "unknown feed-forward kind" + at;
       }
     }
   }
-  if (d.norm_place != HB_NORM_OF_SUM && d.norm_place != HB_NORM_OF_OUTPUT) return "unknown norm_place";
+  if (d.norm_place != HB_NORM_OF_SUM && d.norm_place != HB_NORM_OF_OUTPUT && d.norm_place != HB_NORM_BOTH_SIDES) return "unknown norm_place";
+  if (d.norm_kind != HB_NORM_RMS && d.norm_kind != HB_NORM_TANH) return "unknown norm_kind";
+  if (d.norm_kind == HB_NORM_TANH && d.norm_place == HB_NORM_OF_SUM) return "tanh norms of the sum are unsupported";
+  if (d.norm_kind == HB_NORM_TANH && !d.plain_gains) return "tanh norms store their gains plainly";
+  if (d.norm_kind == HB_NORM_TANH)
+    for (int i = 0; i < d.n_layers; ++i)
+      if (L[i].ff > 0 && L[i].ff_kind == HB_FF_CLAMPED) return "tanh norms with a biased feed-forward are unsupported";
   return "";
 }
 
@@ -258,10 +285,20 @@ static size_t carve_stack(Model* m, const hb_stack_desc& d, const hb_layer_desc*
   };
   const size_t W = d.width, V = d.vocab;
   const float gain_fill = d.plain_gains ? 1.f : 0.f;  // neutral value of a stored residual-norm gain
+  const bool tanh_norm = d.norm_kind == HB_NORM_TANH, both = d.norm_place == HB_NORM_BOTH_SIDES;
+  // a norm of the stream: its gain, and for tanh norms the offset vector and the scalar behind it in one block
+  auto norm_block = [&](const std::string& name) -> uint8_t* {
+    uint8_t* p = take(tanh_norm ? 2 * W + 1 : W);
+    put(name, p, 0, W, 1, true, gain_fill);
+    if (tanh_norm) {
+      put(name + ".b", p ? p + W * es : nullptr, 0, W, 1, true, 0.f);
+      put(name + ".alpha", p ? p + 2 * W * es : nullptr, 0, 1, 1, true, 1.f);
+    }
+    return p;
+  };
   uint8_t* embed = take(V * W);
   put("embed", embed, 0, V, W);
-  uint8_t* embed_norm = d.embed_norm ? take(W) : nullptr;
-  if (d.embed_norm) put("embed.norm", embed_norm, 0, W, 1, true, gain_fill);
+  uint8_t* embed_norm = d.embed_norm ? norm_block("embed.norm") : nullptr;
   if (m) {
     m->s_embed = embed;
     m->s_embed_norm = embed_norm;
@@ -277,10 +314,43 @@ static size_t carve_stack(Model* m, const hb_stack_desc& d, const hb_layer_desc*
     const std::string p = "l" + std::to_string(i) + ".";
     StackLayerW w;
     const size_t H = l.heads, Dk = l.dim, Dv = l.vdim;
-    uint8_t* n1 = take(W);
-    put(p + "norm1", n1, 0, W, 1, true, gain_fill);
-    w.norm1 = n1;
-    if (l.mixer == HB_MIXER_GLA) {
+    w.norm1 = norm_block(p + "norm1");
+    if (both) w.norm1b = norm_block(p + "norm1b");
+    if (l.mixer == HB_MIXER_DELTA) {
+      const size_t G = l.kv_heads, C = 2 * G * Dk + H * Dv, taps = l.conv_taps;
+      w.off_q = 0;
+      w.off_k = (int)(G * Dk);
+      w.off_v = (int)(2 * G * Dk);
+      w.off_g = (int)(2 * G * Dk + H * Dv);
+      w.off_b = (int)(2 * G * Dk + 2 * H * Dv);
+      w.off_a = w.off_b + (int)H;
+      w.n_in = w.off_a + (int)H;
+      uint8_t* in = take((size_t)w.n_in * W);
+      w.w_in = in;
+      put(p + "mix.q", in, w.off_q, G * Dk, W);
+      put(p + "mix.k", in, w.off_k, G * Dk, W);
+      put(p + "mix.v", in, w.off_v, H * Dv, W);
+      put(p + "mix.g", in, w.off_g, H * Dv, W);
+      put(p + "mix.b", in, w.off_b, H, W);
+      put(p + "mix.a", in, w.off_a, H, W);
+      uint8_t* cw = take(C * taps);
+      put(p + "mix.q.conv", cw, 0, G * Dk, taps);
+      put(p + "mix.k.conv", cw, G * Dk, G * Dk, taps);
+      put(p + "mix.v.conv", cw, 2 * G * Dk, H * Dv, taps);
+      uint8_t* adt = take(2 * H);
+      put(p + "mix.A_log", adt, 0, H, 1, false, 1.f, true);
+      put(p + "mix.dt_bias", adt ? adt + H * es : nullptr, 0, H, 1, false, 1.f, true);
+      uint8_t* hn = take(Dv);
+      uint8_t* o = take(W * H * Dv);
+      put(p + "mix.norm", hn, 0, Dv, 1, true, 1.f);
+      put(p + "mix.o", o, 0, W, H * Dv);
+      w.conv_w = cw; w.a_dt = adt; w.hnorm = hn; w.wo = o;
+      if (m) {
+        w.state_off = m->state_floats;
+        w.tail_off = w.state_off + H * Dk * Dv;
+        m->state_floats += H * Dk * Dv + (taps - 1) * C;
+      }
+    } else if (l.mixer == HB_MIXER_GLA) {
       const size_t r = l.decay_rank;
       w.off_q = 0;
       w.off_k = (int)(H * Dk);
@@ -322,6 +392,33 @@ static size_t carve_stack(Model* m, const hb_stack_desc& d, const hb_layer_desc*
       put(p + "mix.k", in, w.off_k, G * Dk, W);
       if (own_v) put(p + "mix.v", in, w.off_v, G * Dv, W);
       if (gated) put(p + "mix.g", in, w.off_g, H, W);
+      if (l.attn_flags & HB_ATTN_QKV_BIAS) {
+        uint8_t* b = take((size_t)w.n_in);
+        w.b_in = b;
+        put(p + "mix.q.b", b ? b + (size_t)w.off_q * es : nullptr, 0, H * Dk, 1, false, 1.f, true);
+        put(p + "mix.k.b", b ? b + (size_t)w.off_k * es : nullptr, 0, G * Dk, 1, false, 1.f, true);
+        if (own_v) put(p + "mix.v.b", b ? b + (size_t)w.off_v * es : nullptr, 0, G * Dv, 1, false, 1.f, true);
+      }
+      if (l.attn_flags & HB_ATTN_QK_PROJ_NORM) {
+        uint8_t* gn = take((H + G) * Dk);
+        w.qk_gain = gn;
+        put(p + "mix.q.norm", gn, 0, H * Dk, 1, true, 1.f);
+        put(p + "mix.k.norm", gn ? gn + H * Dk * es : nullptr, 0, G * Dk, 1, true, 1.f);
+      }
+      if (l.attn_flags & HB_ATTN_LEARNED_SINK) {
+        uint8_t* sk = take(H);
+        w.sink = sk;
+        put(p + "mix.sink", sk, 0, H, 1, false, 1.f, true);
+      }
+      if (l.attn_flags & HB_ATTN_V_BLEND) {
+        uint8_t* vm = take(1);
+        w.vmix = vm;
+        put(p + "mix.vmix", vm, 0, 1, 1, false, 1.f, true);
+        w.blend_role = 2;
+        bool earlier = false;
+        for (int j = 0; j < i; ++j) earlier |= L[j].mixer == HB_MIXER_GQA && (L[j].attn_flags & HB_ATTN_V_BLEND);
+        if (!earlier) w.blend_role = 1;
+      }
       uint8_t* o = take(W * H * Dv);
       put(p + "mix.o", o, 0, W, H * Dv);
       w.wo = o;
@@ -370,15 +467,24 @@ static size_t carve_stack(Model* m, const hb_stack_desc& d, const hb_layer_desc*
     }
     if (l.ff > 0 && l.ff_kind == HB_FF_MOE) {
       const size_t Fn = l.ff, E = l.experts, R = (size_t)l.experts + l.identity_experts;
-      uint8_t* n2 = take(W);
+      uint8_t* n2 = norm_block(p + "norm2");
+      if (both) w.norm2b = norm_block(p + "norm2b");
       uint8_t* router = take(std::max<size_t>(R, 64) * W);  // at least one MMA tile of rows; the arena is zeroed at load
       uint8_t* corr = take(R);
       uint8_t* gu = take(E * 2 * Fn * W);
       uint8_t* dn = take(E * W * Fn);
-      put(p + "norm2", n2, 0, W, 1, true, gain_fill);
       put(p + "mlp.router", router, 0, R, W);
       put(p + "mlp.correction", corr, 0, R, 1, false, 1.f, true);
-      const bool packed = !d.compute_f32 && Fn % 128 == 0;
+      if (l.shared_ff > 0) {
+        const size_t Fs = l.shared_ff;
+        uint8_t* sg = take(2 * Fs * W);
+        uint8_t* sd = take(W * Fs);
+        put(p + "mlp.shared.gate", sg, 0, Fs, W);
+        put(p + "mlp.shared.up", sg, Fs, Fs, W);
+        put(p + "mlp.shared.down", sd, 0, W, Fs);
+        w.w_gu_sh = sg; w.w_down_sh = sd;
+      }
+      const bool packed = !d.compute_f32 && Fn % 128 == 0 && l.expert_kind == HB_EXPERT_SILU;
       for (size_t e = 0; e < E; ++e) {
         const std::string pe = p + "mlp.e" + std::to_string(e) + ".";
         put(pe + "gate", gu, e * 2 * Fn, Fn, W, false, 1.f, false, packed ? 1 : 0);
@@ -387,13 +493,13 @@ static size_t carve_stack(Model* m, const hb_stack_desc& d, const hb_layer_desc*
       }
       w.gu_packed = packed;
       w.norm2 = n2; w.router = router; w.correction = corr; w.w_gu = gu; w.w_down = dn;
-    } else if (l.ff > 0 && l.ff_kind == HB_FF_GELU_TANH) {
+    } else if (l.ff > 0 && (l.ff_kind == HB_FF_GELU_TANH || l.ff_kind == HB_FF_SILU)) {
       const size_t Fn = l.ff;
-      uint8_t* n2 = take(W);
+      uint8_t* n2 = norm_block(p + "norm2");
+      if (both) w.norm2b = norm_block(p + "norm2b");
       uint8_t* gu = take(2 * Fn * W);
       uint8_t* dn = take(W * Fn);
       const bool packed = !d.compute_f32 && Fn % 128 == 0;
-      put(p + "norm2", n2, 0, W, 1, true, gain_fill);
       put(p + "mlp.gate", gu, 0, Fn, W, false, 1.f, false, packed ? 1 : 0);
       put(p + "mlp.up", gu, packed ? 0 : Fn, Fn, W, false, 1.f, false, packed ? 2 : 0);
       put(p + "mlp.down", dn, 0, W, Fn);
@@ -401,12 +507,12 @@ static size_t carve_stack(Model* m, const hb_stack_desc& d, const hb_layer_desc*
       w.norm2 = n2; w.w_gu = gu; w.w_down = dn;
     } else if (l.ff > 0) {
       const size_t Fn = l.ff;
-      uint8_t* n2 = take(W);
+      uint8_t* n2 = norm_block(p + "norm2");
+      if (both) w.norm2b = norm_block(p + "norm2b");
       uint8_t* gu = take(2 * Fn * W);
       uint8_t* bgu = take(2 * Fn);
       uint8_t* dn = take(W * Fn);
       uint8_t* bdn = take(W);
-      put(p + "norm2", n2, 0, W, 1, true, gain_fill);
       put(p + "mlp.gate", gu, 0, Fn, W);
       put(p + "mlp.up", gu, Fn, Fn, W);
       put(p + "mlp.gate.b", bgu, 0, Fn, 1, false, 1.f, true);
@@ -417,9 +523,8 @@ static size_t carve_stack(Model* m, const hb_stack_desc& d, const hb_layer_desc*
     }
     if (m) m->sw[i] = w;
   }
-  uint8_t* fn = take(W);
+  uint8_t* fn = norm_block("final.norm");
   uint8_t* head = take(V * W);
-  put("final.norm", fn, 0, W, 1, true, gain_fill);
   put("head", head, 0, V, W);
   if (m) {
     m->s_final_norm = fn;

@@ -25,14 +25,25 @@ struct BertLayerW {
 // Projections that read the same input are stacked into one weight (w_in) so one GEMM produces all of them:
 //   GLA:    rows [q | k | v | g | a1]            LATENT: rows [dq | dkv (own cache only) | g]
 //   GQA:    rows [q | k | v (unless the values are the keys) | g (one row per head, when gated)]
+//   DELTA:  rows [q | k | v | g | b (one row per head) | a (one row per head)]
+// Norms of kind HB_NORM_TANH are blocks [gain (width) | offset (width) | alpha (1)] behind one pointer.
 struct StackLayerW {
   void *norm1 = nullptr, *norm2 = nullptr;
+  void *norm1b = nullptr, *norm2b = nullptr;  // HB_NORM_BOTH_SIDES: the norms of the sublayers' outputs (norm1 / norm2: of their inputs)
   void* w_in = nullptr;
   int n_in = 0;
   int off_q = 0, off_k = 0, off_v = 0, off_g = 0, off_a1 = 0, off_dq = 0, off_dkv = -1;  // columns of the fused projection
   void *a2 = nullptr, *a2b = nullptr, *hnorm = nullptr;                                          // GLA
   void *dq_norm = nullptr, *uq = nullptr, *dkv_norm = nullptr, *uk = nullptr, *uv = nullptr, *sink = nullptr;  // LATENT
   void* ukT = nullptr;  // LATENT, bf16 mode: [heads][kv_rank][dim] copy of uk (built after load; no checkpoint tensor)
+  void* b_in = nullptr;     // GQA with biases: [n_in] in the order of w_in's rows
+  void* qk_gain = nullptr;  // GQA with whole-projection norms: [heads * dim | kv_heads * dim]
+  void* vmix = nullptr;     // GQA with blended values: the blend weight (1 element)
+  int blend_role = 0;       // 0: no blending; 1: the first blending layer (keeps its values, publishes them); 2: blends
+  int off_b = 0, off_a = 0;                      // DELTA: columns of the write-strength and decay rows
+  void *conv_w = nullptr, *a_dt = nullptr;       // DELTA: [2 kv_heads dim + heads vdim][taps] in q, k, v order; [A_log (heads) | dt_bias (heads)]
+  size_t tail_off = 0;                           // DELTA: float offset of the [taps - 1][channels] convolution inputs inside a state slot
+  void *w_gu_sh = nullptr, *w_down_sh = nullptr;  // mixture of experts: the unit every token uses, rows [gate | up] and down
   void* wo = nullptr;
   void *w_gu = nullptr, *b_gu = nullptr, *w_down = nullptr, *b_down = nullptr;  // feed-forward: rows [gate | up]
   size_t state_off = 0;  // GLA: float offset of this layer's [heads][dim][vdim] block inside a state slot

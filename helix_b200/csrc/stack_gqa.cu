@@ -180,6 +180,79 @@ __global__ void __launch_bounds__(256) gqa_prep_vec_kernel(GqaPrepArgs a) {
   }
 }
 
+// One block per token, for the options the warp-per-head kernels do not take: projection biases, a norm over the whole q (and
+// k) projection with a gain per entry, values blended with an earlier layer's.  Order: bias, rotation, norm.
+// dynamic smem: the token's q | k rows [(H + G) * D] + per-head factors [H + G]
+template <typename CT>
+__global__ void __launch_bounds__(256) gqa_prep_token_kernel(GqaPrepArgs a) {
+  extern __shared__ float sm[];
+  __shared__ float red[32];
+  const int t = blockIdx.x;
+  const int nq = a.H * a.D, nk = a.G * a.D, nv = a.G * a.Dv;
+  float* rsh = sm + nq + nk;
+  const float* pr = a.p + (size_t)t * a.ldp;
+  const CT* bias = (const CT*)a.bias;
+  for (int i = threadIdx.x; i < nq + nk; i += blockDim.x) {
+    const int col = i < nq ? a.q_off + i : a.k_off + (i - nq);
+    sm[i] = pr[col] + (bias ? ldf<CT>(bias, col) : 0.f);
+  }
+  __syncthreads();
+  const int half = a.rope_dims / 2;
+  if (half > 0) {
+    for (int u = threadIdx.x; u < (a.H + a.G) * half; u += blockDim.x) {
+      const int head = u / half, i = u % half;
+      const float2 cs = *reinterpret_cast<const float2*>(a.cs + (size_t)t * a.rope_dims + 2 * i);
+      float* hp = sm + (size_t)head * a.D;
+      const int i0 = a.pairing ? 2 * i : i, i1 = a.pairing ? 2 * i + 1 : i + half;
+      const float x = hp[i0], y = hp[i1];
+      hp[i0] = x * cs.x - y * cs.y;
+      hp[i1] = y * cs.x + x * cs.y;
+    }
+    __syncthreads();
+  }
+  float rq = 1.f, rk = 1.f;
+  if (a.proj_norm) {
+    float sq = 0.f, sk = 0.f;
+    for (int i = threadIdx.x; i < nq; i += blockDim.x) sq = fmaf(sm[i], sm[i], sq);
+    for (int i = threadIdx.x; i < nk; i += blockDim.x) sk = fmaf(sm[nq + i], sm[nq + i], sk);
+    sq = block_sum(sq, red);
+    sk = block_sum(sk, red);
+    rq = 1.f / sqrtf(sq / (float)nq + a.eps);
+    rk = 1.f / sqrtf(sk / (float)nk + a.eps);
+  } else if (a.unit_norm) {
+    const int w = threadIdx.x >> 5, l = threadIdx.x & 31;
+    for (int head = w; head < a.H + a.G; head += blockDim.x >> 5) {
+      float ss = 0.f;
+      for (int i = l; i < a.D; i += 32) ss = fmaf(sm[head * a.D + i], sm[head * a.D + i], ss);
+      ss = warp_sum(ss);
+      if (l == 0) rsh[head] = 1.f / sqrtf(ss / (float)a.D + a.eps);
+    }
+    __syncthreads();
+  }
+  const CT* gain = (const CT*)a.qk_gain;
+  for (int i = threadIdx.x; i < nq; i += blockDim.x) {
+    const float v = sm[i] * (a.proj_norm ? rq * ldf<CT>(gain, i) : (a.unit_norm ? rsh[i / a.D] : 1.f));
+    if (a.q) a.q[(size_t)t * a.ldq + i] = v;
+    if (a.q_b16) a.q_b16[(size_t)t * a.ldq + i] = __float2bfloat16(v);
+  }
+  const int slot = a.slots ? a.slots[t] : -1;
+  const size_t page = slot >= 0 ? slot / a.page_size : 0, off = slot >= 0 ? slot % a.page_size : 0;
+  if (slot >= 0) {
+    for (int i = threadIdx.x; i < nk; i += blockDim.x) {
+      const int head = i / a.D;
+      const float v = sm[nq + i] * (a.proj_norm ? rk * ldf<CT>(gain, nq + i) : (a.unit_norm ? rsh[a.H + head] : 1.f));
+      stf<CT>((CT*)a.k_cache, ((page * a.G + head) * a.page_size + off) * a.D + i % a.D, v);
+    }
+  }
+  const float lam = a.blend_role == 2 ? ldf<CT>((const CT*)a.vmix, 0) : 0.f;
+  for (int i = threadIdx.x; i < nv; i += blockDim.x) {
+    float v = pr[a.v_off + i] + (bias ? ldf<CT>(bias, a.v_off + i) : 0.f);
+    if (a.blend_role == 1) a.v_first[(size_t)t * nv + i] = v;
+    else if (a.blend_role == 2) v = (1.f - lam) * v + lam * a.v_first[(size_t)t * nv + i];
+    if (slot >= 0) stf<CT>((CT*)a.v_cache, ((page * a.G + i / a.Dv) * a.page_size + off) * a.Dv + i % a.Dv, v);
+  }
+}
+
 // One block per (token, kv head, group of up to kHG of its query heads): the heads of a group read the same key and value
 // rows, so one pass over them serves the group.
 //   scores:       one warp per key, lanes stride the row, HG dot products per loaded row
@@ -220,6 +293,11 @@ __global__ void __launch_bounds__(kAttThreads) gqa_attn_kernel(GqaAttnArgs a, in
   const int w = threadIdx.x >> 5, l = threadIdx.x & 31, nw = blockDim.x >> 5;
   const CT* kc = (const CT*)a.k_cache;
   const CT* vc = (const CT*)a.v_cache;
+  const float cap = a.softcap, icap = cap > 0.f ? 1.f / cap : 0.f;
+  auto fin = [&](float sdot) {  // scale, then the optional tanh cap
+    const float v = sdot * a.scale;
+    return cap > 0.f ? cap * tanhf(v * icap) : v;
+  };
   const int lpk = D / 8;  // lanes that cover one bf16 key row with one 16-byte load each
   if (sizeof(CT) == 2 && (D & 7) == 0 && (lpk == 4 || lpk == 8 || lpk == 16 || lpk == 32)) {
     // several keys per warp iteration: sub-warp `sub` of lpk lanes takes key base + sub; partial dot products are added
@@ -248,7 +326,7 @@ __global__ void __launch_bounds__(kAttThreads) gqa_attn_kernel(GqaAttnArgs a, in
       }
       if (live && li == 0) {
 #pragma unroll
-        for (int hh = 0; hh < HG; ++hh) sc[jj * HG + hh] = s[hh] * a.scale;
+        for (int hh = 0; hh < HG; ++hh) sc[jj * HG + hh] = fin(s[hh]);
       }
     }
   } else if (sizeof(CT) == 2 && (D & 7) == 0) {
@@ -274,7 +352,7 @@ __global__ void __launch_bounds__(kAttThreads) gqa_attn_kernel(GqaAttnArgs a, in
       for (int hh = 0; hh < HG; ++hh) s[hh] = warp_sum(s[hh]);
       if (l == 0) {
 #pragma unroll
-        for (int hh = 0; hh < HG; ++hh) sc[jj * HG + hh] = s[hh] * a.scale;
+        for (int hh = 0; hh < HG; ++hh) sc[jj * HG + hh] = fin(s[hh]);
       }
     }
   } else {
@@ -290,14 +368,17 @@ __global__ void __launch_bounds__(kAttThreads) gqa_attn_kernel(GqaAttnArgs a, in
       for (int hh = 0; hh < HG; ++hh) s[hh] = warp_sum(s[hh]);
       if (l == 0) {
 #pragma unroll
-        for (int hh = 0; hh < HG; ++hh) sc[jj * HG + hh] = s[hh] * a.scale;
+        for (int hh = 0; hh < HG; ++hh) sc[jj * HG + hh] = fin(s[hh]);
       }
     }
   }
   __syncthreads();
-  float mx[HG], inv[HG];
+  float mx[HG], inv[HG], snk[HG];
 #pragma unroll
-  for (int hh = 0; hh < HG; ++hh) mx[hh] = a.unit_sink ? 0.f : -INFINITY;
+  for (int hh = 0; hh < HG; ++hh) {  // a sink is a key without a value: the unit's score is 0, a learned one's is stored per head
+    snk[hh] = a.sink ? ldf<CT>((const CT*)a.sink, h0 + (hh < nh ? hh : 0)) : (a.unit_sink ? 0.f : -INFINITY);
+    mx[hh] = snk[hh];
+  }
   for (int jj = threadIdx.x; jj < n; jj += blockDim.x) {
     const float4 v = *reinterpret_cast<const float4*>(sc + jj * HG);
     mx[0] = fmaxf(mx[0], v.x); mx[1] = fmaxf(mx[1], v.y); mx[2] = fmaxf(mx[2], v.z); mx[3] = fmaxf(mx[3], v.w);
@@ -328,7 +409,7 @@ __global__ void __launch_bounds__(kAttThreads) gqa_attn_kernel(GqaAttnArgs a, in
   __syncthreads();  // also publishes the exponentials in sc[]
 #pragma unroll
   for (int hh = 0; hh < HG; ++hh) {
-    const float tot = warp_sum(l < nw ? red[l * HG + hh] : 0.f) + (a.unit_sink ? expf(-mx[hh]) : 0.f);
+    const float tot = warp_sum(l < nw ? red[l * HG + hh] : 0.f) + ((a.unit_sink || a.sink) ? expf(snk[hh] - mx[hh]) : 0.f);
     float gate = 1.f;
     if (a.gate && hh < nh) gate = sigmoidf_(a.gate[(size_t)t * a.ldg + h0 + hh]);
     inv[hh] = gate / tot;
@@ -481,12 +562,22 @@ cudaError_t stack_gqa_init() {
   if ((e = cudaFuncSetAttribute(gqa_attn_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, big)) != cudaSuccess) return e;
   if ((e = cudaFuncSetAttribute(gqa_prep_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, 72 * 1024)) != cudaSuccess) return e;
   if ((e = cudaFuncSetAttribute(gqa_prep_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 72 * 1024)) != cudaSuccess) return e;
+  if ((e = cudaFuncSetAttribute(gqa_prep_token_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024)) != cudaSuccess) return e;
+  if ((e = cudaFuncSetAttribute(gqa_prep_token_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024)) != cudaSuccess) return e;
   return cudaSuccess;
 }
 
 cudaError_t gqa_prep(cudaStream_t s, const GqaPrepArgs& a) {
   if (a.T <= 0) return cudaSuccess;
   if (a.rope_dims % 2 || a.rope_dims > a.D || (a.rope_dims > 0 && !a.cs)) return cudaErrorInvalidValue;
+  if (a.bias || a.proj_norm || a.blend_role) {
+    if ((a.proj_norm && !a.qk_gain) || (a.blend_role && !a.v_first) || (a.blend_role == 2 && !a.vmix)) return cudaErrorInvalidValue;
+    const size_t smem = ((size_t)(a.H + a.G) * a.D + a.H + a.G) * 4;
+    if (smem > 100 * 1024) return cudaErrorInvalidValue;
+    if (a.f32) gqa_prep_token_kernel<float><<<a.T, 256, smem, s>>>(a);
+    else gqa_prep_token_kernel<bf16><<<a.T, 256, smem, s>>>(a);
+    return cudaGetLastError();
+  }
   const bool aligned = (a.D & 3) == 0 && a.D <= 512 && (a.ldp & 3) == 0 && (a.q_off & 3) == 0 && (a.k_off & 3) == 0 && (a.ldq & 3) == 0 &&
                        ((uintptr_t)a.p & 15) == 0 && ((uintptr_t)a.q & 15) == 0 && ((uintptr_t)a.q_b16 & 7) == 0 &&
                        ((uintptr_t)a.k_cache & 15) == 0 && ((uintptr_t)a.v_cache & 15) == 0 && ((uintptr_t)a.cs & 15) == 0 &&

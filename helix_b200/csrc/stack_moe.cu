@@ -15,12 +15,21 @@ namespace {
 __device__ __forceinline__ float gelu_tanh_(float z) {
   return 0.5f * z * (1.f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
 }
-__device__ __forceinline__ float glu_act(float z, int act) { return act == GLU_GELU_TANH ? gelu_tanh_(z) : z * sigmoidf_(z); }
+// one gated pair: act(gate) * up, or the clamped form min(g, limit) sigmoid(1.702 g) (clamp(u, +-limit) + 1)
+__device__ __forceinline__ float glu_pair(float g, float u, int act, float limit) {
+  if (act == GLU_CLAMPED) {
+    g = fminf(g, limit);
+    u = fminf(fmaxf(u, -limit), limit);
+    return g * sigmoidf_(1.702f * g) * (u + 1.f);
+  }
+  return (act == GLU_GELU_TANH ? gelu_tanh_(g) : g * sigmoidf_(g)) * u;
+}
 
 // VEC = 4: F and ldg are multiples of four (16-byte loads and stores).  PACKED: gate j of tile i sits at column 256 i + j and
 // its up at 256 i + 128 + j (weights stored per 256-row tile as [128 gate | 128 up]); the output column is 128 i + j
 template <int VEC, bool PACKED>
-__global__ void gated_unit_kernel(const float* __restrict__ gu, long ldg, int act, float* __restrict__ out, bf16* __restrict__ outb, int F) {
+__global__ void gated_unit_kernel(const float* __restrict__ gu, long ldg, int act, float* __restrict__ out, bf16* __restrict__ outb, int F,
+                                  float limit) {
   const size_t t = blockIdx.x;
   const int j = (blockIdx.y * blockDim.x + threadIdx.x) * VEC;
   if (j >= F) return;
@@ -28,7 +37,8 @@ __global__ void gated_unit_kernel(const float* __restrict__ gu, long ldg, int ac
   if (VEC == 4) {
     const float4 g = *reinterpret_cast<const float4*>(gu + t * ldg + gi);
     const float4 u = *reinterpret_cast<const float4*>(gu + t * ldg + ui);
-    const float v0 = glu_act(g.x, act) * u.x, v1 = glu_act(g.y, act) * u.y, v2 = glu_act(g.z, act) * u.z, v3 = glu_act(g.w, act) * u.w;
+    const float v0 = glu_pair(g.x, u.x, act, limit), v1 = glu_pair(g.y, u.y, act, limit), v2 = glu_pair(g.z, u.z, act, limit),
+                v3 = glu_pair(g.w, u.w, act, limit);
     if (out) *reinterpret_cast<float4*>(out + t * F + j) = make_float4(v0, v1, v2, v3);
     if (outb) {
       __nv_bfloat162 lo = __floats2bfloat162_rn(v0, v1), hi = __floats2bfloat162_rn(v2, v3);
@@ -38,25 +48,63 @@ __global__ void gated_unit_kernel(const float* __restrict__ gu, long ldg, int ac
       *reinterpret_cast<uint2*>(outb + t * F + j) = pk;
     }
   } else {
-    const float v = glu_act(gu[t * ldg + gi], act) * gu[t * ldg + ui];
+    const float v = glu_pair(gu[t * ldg + gi], gu[t * ldg + ui], act, limit);
     if (out) out[t * F + j] = v;
     if (outb) outb[t * F + j] = __float2bfloat16(v);
   }
 }
 
-// The choice of one token by one warp: zr[R] router logits (global or shared memory), pick[R] scratch in shared memory.
+// The choice of one token by one warp: zr[R] router logits (global or shared memory), pick[2 R] scratch in shared memory
+// (choice scores, then group scores).
 template <typename WT>
 __device__ __forceinline__ void route_one(const float* zr, const WT* __restrict__ corr, int R, int top_k, float* pick,
-                                          int32_t* __restrict__ ids, float* __restrict__ wts, int l) {
-  float mx = -INFINITY;
-  for (int i = l; i < R; i += 32) mx = fmaxf(mx, zr[i]);
-  mx = warp_max(mx);
-  float sum = 0.f;
-  for (int i = l; i < R; i += 32) sum += expf(zr[i] - mx);
-  sum = warp_sum(sum);
-  const float inv = 1.f / sum;
-  for (int i = l; i < R; i += 32) pick[i] = expf(zr[i] - mx) * inv + ldf<WT>(corr, i);
+                                          int32_t* __restrict__ ids, float* __restrict__ wts, int l, const RouteOpts& ro) {
+  float mx = 0.f, inv = 1.f;
+  if (!ro.sigmoid) {
+    mx = -INFINITY;
+    for (int i = l; i < R; i += 32) mx = fmaxf(mx, zr[i]);
+    mx = warp_max(mx);
+    float sum = 0.f;
+    for (int i = l; i < R; i += 32) sum += expf(zr[i] - mx);
+    sum = warp_sum(sum);
+    inv = 1.f / sum;
+  }
+  auto score = [&](int i) { return ro.sigmoid ? sigmoidf_(zr[i]) : expf(zr[i] - mx) * inv; };
+  for (int i = l; i < R; i += 32) pick[i] = score(i) + ldf<WT>(corr, i);
   __syncwarp();
+  if (ro.groups > 1 && ro.keep < ro.groups) {
+    float* gs = pick + R;
+    const int per = R / ro.groups;
+    for (int g = l; g < ro.groups; g += 32) {  // a group scores the sum of its two largest choice scores
+      float a = -INFINITY, b = -INFINITY;
+      for (int i = g * per; i < (g + 1) * per; ++i) {
+        const float v = pick[i];
+        if (v > a) { b = a; a = v; } else if (v > b) { b = v; }
+      }
+      gs[g] = per > 1 ? a + b : a;
+    }
+    __syncwarp();
+    for (int k = 0; k < ro.keep; ++k) {  // the kept groups are marked with -inf (a real score is finite)
+      float best = -INFINITY;
+      int bi = 0x7fffffff;
+      for (int g = l; g < ro.groups; g += 32) {
+        const float v = gs[g];
+        if (v > best) { best = v; bi = g; }
+      }
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+        if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
+      }
+      if (l == 0 && bi < ro.groups) gs[bi] = -INFINITY;
+      __syncwarp();
+    }
+    for (int i = l; i < R; i += 32)
+      if (gs[i / per] != -INFINITY) pick[i] = -INFINITY;  // outputs of dropped groups cannot be chosen
+    __syncwarp();
+  }
+  float wsum = 0.f;
   for (int k = 0; k < top_k; ++k) {
     float best = -INFINITY;
     int bi = 0x7fffffff;
@@ -71,29 +119,37 @@ __device__ __forceinline__ void route_one(const float* zr, const WT* __restrict_
       if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
     }
     if (l == 0) {
+      if (bi >= R) bi = 0;  // fewer eligible outputs than top_k (excluded at load): stay inside the tables
+      const float sc = score(bi);  // the score itself, without the correction
       ids[k] = bi;
-      wts[k] = expf(zr[bi] - mx) * inv;  // the score itself, without the correction
+      wts[k] = sc;
+      wsum += sc;
       pick[bi] = -INFINITY;
     }
     __syncwarp();
   }
+  if (l == 0) {
+    const float f = (ro.renorm ? 1.f / (wsum + 1e-20f) : 1.f) * ro.scale;
+    if (f != 1.f)
+      for (int k = 0; k < top_k; ++k) wts[k] *= f;
+  }
 }
 
-// One warp per token.  dynamic smem: per warp R floats (the choice scores while the top-k is taken)
+// One warp per token.  dynamic smem: per warp 2 R floats (the choice scores while the top-k is taken, group scores)
 template <typename WT>
 __global__ void __launch_bounds__(128) moe_route_kernel(const float* __restrict__ z, long ldz, const WT* __restrict__ corr, int R,
-                                                        int top_k, int32_t* __restrict__ ids, float* __restrict__ wts, int T) {
+                                                        int top_k, int32_t* __restrict__ ids, float* __restrict__ wts, int T, RouteOpts ro) {
   extern __shared__ float sm[];
   const int w = threadIdx.x >> 5, l = threadIdx.x & 31;
   const int t = blockIdx.x * (blockDim.x >> 5) + w;
   if (t >= T) return;
-  route_one<WT>(z + (size_t)t * ldz, corr, R, top_k, sm + (size_t)w * R, ids + (size_t)t * top_k, wts + (size_t)t * top_k, l);
+  route_one<WT>(z + (size_t)t * ldz, corr, R, top_k, sm + (size_t)w * 2 * R, ids + (size_t)t * top_k, wts + (size_t)t * top_k, l, ro);
 }
 
 // Router logits and choice in one kernel: the router's rows stay in shared memory, every warp takes tokens in turn and
 // forms the R dot products of its token's fp32 row (lanes stride the row four entries at a time, kRouterRT outputs per pass
 // so that a pass keeps many independent loads in flight), then chooses.
-// dynamic smem: router [R][W] of WT | per warp: logits [R] + scratch [R]
+// dynamic smem: router [R][W] of WT | per warp: logits [R] + scratch [2 R]
 constexpr int kRouterWarps = 16;
 constexpr int kRouterRT = 16;
 __device__ __forceinline__ float4 ld4(const float* p) { return *reinterpret_cast<const float4*>(p); }
@@ -106,7 +162,7 @@ __device__ __forceinline__ float4 ld4(const bf16* p) {
 template <typename WT>
 __global__ void __launch_bounds__(kRouterWarps * 32) moe_router_kernel(const float* __restrict__ x, const WT* __restrict__ router,
                                                                        const WT* __restrict__ corr, int R, int W, int top_k,
-                                                                       int32_t* __restrict__ ids, float* __restrict__ wts, int T) {
+                                                                       int32_t* __restrict__ ids, float* __restrict__ wts, int T, RouteOpts ro) {
   extern __shared__ float sm[];
   WT* rw = reinterpret_cast<WT*>(sm);
   float* zs = sm + ((size_t)R * W * sizeof(WT) + 15) / 16 * 4;
@@ -119,7 +175,7 @@ __global__ void __launch_bounds__(kRouterWarps * 32) moe_router_kernel(const flo
   }
   __syncthreads();
   const int w = threadIdx.x >> 5, l = threadIdx.x & 31;
-  float* z = zs + (size_t)w * 2 * R;
+  float* z = zs + (size_t)w * 3 * R;
   for (int t = blockIdx.x * kRouterWarps + w; t < T; t += gridDim.x * kRouterWarps) {
     const float* xr = x + (size_t)t * W;
     for (int r0 = 0; r0 < R; r0 += kRouterRT) {
@@ -151,17 +207,17 @@ __global__ void __launch_bounds__(kRouterWarps * 32) moe_router_kernel(const flo
       }
     }
     __syncwarp();
-    route_one<WT>(z, corr, R, top_k, z + R, ids + (size_t)t * top_k, wts + (size_t)t * top_k, l);
+    route_one<WT>(z, corr, R, top_k, z + R, ids + (size_t)t * top_k, wts + (size_t)t * top_k, l, ro);
     __syncwarp();
   }
 }
 
 // Steps of few tokens: one block per token, warp w forms the outputs w, w + warps, ... straight from the router's rows in
-// global memory (each row is read once per block), warp 0 chooses.  dynamic smem: logits [R] + scratch [R]
+// global memory (each row is read once per block), warp 0 chooses.  dynamic smem: logits [R] + scratch [2 R]
 template <typename WT>
 __global__ void __launch_bounds__(kRouterWarps * 32) moe_router_small_kernel(const float* __restrict__ x, const WT* __restrict__ router,
                                                                              const WT* __restrict__ corr, int R, int W, int top_k,
-                                                                             int32_t* __restrict__ ids, float* __restrict__ wts) {
+                                                                             int32_t* __restrict__ ids, float* __restrict__ wts, RouteOpts ro) {
   extern __shared__ float sm[];
   const int t = blockIdx.x, w = threadIdx.x >> 5, l = threadIdx.x & 31;
   const float* xr = x + (size_t)t * W;
@@ -181,11 +237,11 @@ __global__ void __launch_bounds__(kRouterWarps * 32) moe_router_small_kernel(con
     if (l == 0) sm[r] = acc;
   }
   __syncthreads();
-  if (w == 0) route_one<WT>(sm, corr, R, top_k, sm + R, ids + (size_t)t * top_k, wts + (size_t)t * top_k, l);
+  if (w == 0) route_one<WT>(sm, corr, R, top_k, sm + R, ids + (size_t)t * top_k, wts + (size_t)t * top_k, l, ro);
 }
 
 // bf16 in, bf16 out: h[t, j] = act(gu[t, j]) * gu[t, F + j], eight columns per thread (F and ldg multiples of eight)
-__global__ void gated_unit_b16_kernel(const bf16* __restrict__ gu, long ldg, int act, bf16* __restrict__ out, int F) {
+__global__ void gated_unit_b16_kernel(const bf16* __restrict__ gu, long ldg, int act, bf16* __restrict__ out, int F, float limit) {
   const size_t t = blockIdx.x;
   const int j = (blockIdx.y * blockDim.x + threadIdx.x) * 8;
   if (j >= F) return;
@@ -198,7 +254,7 @@ __global__ void gated_unit_b16_kernel(const bf16* __restrict__ gu, long ldg, int
 #pragma unroll
   for (int e = 0; e < 4; ++e) {
     const float2 g = __bfloat1622float2(g2[e]), u = __bfloat1622float2(u2[e]);
-    o2[e] = __floats2bfloat162_rn(glu_act(g.x, act) * u.x, glu_act(g.y, act) * u.y);
+    o2[e] = __floats2bfloat162_rn(glu_pair(g.x, u.x, act, limit), glu_pair(g.y, u.y, act, limit));
   }
   *reinterpret_cast<uint4*>(out + t * F + j) = o4;
 }
@@ -229,7 +285,7 @@ template <typename WT>
 __global__ void __launch_bounds__(256) moe_expert_rows_kernel(const float* __restrict__ x, const bf16* __restrict__ xb,
                                                               const WT* __restrict__ w_gu, const WT* __restrict__ w_down,
                                                               const int32_t* __restrict__ ids, int E, int F, int W,
-                                                              float* __restrict__ y, int packed) {
+                                                              float* __restrict__ y, int packed, int act, float limit) {
   extern __shared__ float sm[];
   const int t = blockIdx.x;
   const size_t item = (size_t)t * gridDim.y + blockIdx.y;  // (token, choice)
@@ -246,7 +302,7 @@ __global__ void __launch_bounds__(256) moe_expert_rows_kernel(const float* __res
     const float g = warp_dot<WT>(gu + gr * W, xs, W, l);
     const float u = warp_dot<WT>(gu + ur * W, xs, W, l);
     if (l == 0) {
-      float v = g * sigmoidf_(g) * u;
+      float v = glu_pair(g, u, act, limit);
       if (xb) v = __bfloat162float(__float2bfloat16(v));
       hs[f] = v;
     }
@@ -260,10 +316,10 @@ __global__ void __launch_bounds__(256) moe_expert_rows_kernel(const float* __res
 }
 
 __global__ void moe_combine_kernel(const float* __restrict__ x, const float* __restrict__ y, const int32_t* __restrict__ ids,
-                                   const float* __restrict__ wts, int top_k, int E, float* __restrict__ out, int W) {
+                                   const float* __restrict__ wts, int top_k, int E, float* out, int W, const float* add) {
   const int t = blockIdx.x;
   for (int c = threadIdx.x; c < W; c += blockDim.x) {
-    float acc = 0.f;
+    float acc = add ? add[(size_t)t * W + c] : 0.f;
     for (int k = 0; k < top_k; ++k) {
       const size_t item = (size_t)t * top_k + k;
       const float v = ids[item] < E ? y[item * W + c] : x[(size_t)t * W + c];
@@ -371,10 +427,10 @@ __global__ void __launch_bounds__(128) moe_gather_kernel(const bf16* __restrict_
 }
 
 __global__ void moe_combine_rows_kernel(const float* __restrict__ x, const bf16* __restrict__ y, const int32_t* __restrict__ row_of,
-                                        const float* __restrict__ wts, int top_k, float* __restrict__ out, int W) {
+                                        const float* __restrict__ wts, int top_k, float* out, int W, const float* add) {
   const int t = blockIdx.x;
   for (int c = threadIdx.x; c < W; c += blockDim.x) {
-    float acc = 0.f;
+    float acc = add ? add[(size_t)t * W + c] : 0.f;
     for (int k = 0; k < top_k; ++k) {
       const size_t item = (size_t)t * top_k + k;
       const int r = row_of[item];
@@ -414,9 +470,9 @@ cudaError_t moe_gather_rows(cudaStream_t s, const bf16* x16, int W, const int32_
 }
 
 cudaError_t moe_combine_rows(cudaStream_t s, const float* x, const bf16* y, const int32_t* row_of, const float* wts, int top_k,
-                             float* out, int T, int W) {
+                             float* out, int T, int W, const float* add) {
   if (T <= 0) return cudaSuccess;
-  moe_combine_rows_kernel<<<T, 256, 0, s>>>(x, y, row_of, wts, top_k, out, W);
+  moe_combine_rows_kernel<<<T, 256, 0, s>>>(x, y, row_of, wts, top_k, out, W, add);
   return cudaGetLastError();
 }
 
@@ -430,71 +486,71 @@ cudaError_t stack_moe_init() {
   return cudaSuccess;
 }
 
-cudaError_t gated_unit(cudaStream_t s, const float* gu, long ldg, int act, float* out, bf16* outb, int T, int F, bool packed) {
+cudaError_t gated_unit(cudaStream_t s, const float* gu, long ldg, int act, float* out, bf16* outb, int T, int F, bool packed, float limit) {
   if (T <= 0) return cudaSuccess;
   if (packed && F % 128) return cudaErrorInvalidValue;
   const bool vec = F % 4 == 0 && ldg % 4 == 0 && ((uintptr_t)gu & 15) == 0 && ((uintptr_t)out & 15) == 0 && ((uintptr_t)outb & 7) == 0;
   dim3 grid(T, ((vec ? F / 4 : F) + 255) / 256);
-  if (vec && packed) gated_unit_kernel<4, true><<<grid, 256, 0, s>>>(gu, ldg, act, out, outb, F);
-  else if (vec) gated_unit_kernel<4, false><<<grid, 256, 0, s>>>(gu, ldg, act, out, outb, F);
-  else if (packed) gated_unit_kernel<1, true><<<grid, 256, 0, s>>>(gu, ldg, act, out, outb, F);
-  else gated_unit_kernel<1, false><<<grid, 256, 0, s>>>(gu, ldg, act, out, outb, F);
+  if (vec && packed) gated_unit_kernel<4, true><<<grid, 256, 0, s>>>(gu, ldg, act, out, outb, F, limit);
+  else if (vec) gated_unit_kernel<4, false><<<grid, 256, 0, s>>>(gu, ldg, act, out, outb, F, limit);
+  else if (packed) gated_unit_kernel<1, true><<<grid, 256, 0, s>>>(gu, ldg, act, out, outb, F, limit);
+  else gated_unit_kernel<1, false><<<grid, 256, 0, s>>>(gu, ldg, act, out, outb, F, limit);
   return cudaGetLastError();
 }
 
 cudaError_t moe_route(cudaStream_t s, const float* z, long ldz, const void* corr, bool f32, int R, int top_k, int32_t* ids, float* wts,
-                      int T) {
+                      int T, const RouteOpts& ro) {
   if (T <= 0) return cudaSuccess;
-  if (R <= 0 || top_k <= 0 || top_k > R || R > 1024) return cudaErrorInvalidValue;
-  const size_t smem = (size_t)4 * R * 4;
-  if (f32) moe_route_kernel<float><<<(T + 3) / 4, 128, smem, s>>>(z, ldz, (const float*)corr, R, top_k, ids, wts, T);
-  else moe_route_kernel<bf16><<<(T + 3) / 4, 128, smem, s>>>(z, ldz, (const bf16*)corr, R, top_k, ids, wts, T);
+  if (R <= 0 || top_k <= 0 || top_k > R || R > 1024 || (ro.groups > 1 && R % ro.groups)) return cudaErrorInvalidValue;
+  const size_t smem = (size_t)4 * 2 * R * 4;
+  if (f32) moe_route_kernel<float><<<(T + 3) / 4, 128, smem, s>>>(z, ldz, (const float*)corr, R, top_k, ids, wts, T, ro);
+  else moe_route_kernel<bf16><<<(T + 3) / 4, 128, smem, s>>>(z, ldz, (const bf16*)corr, R, top_k, ids, wts, T, ro);
   return cudaGetLastError();
 }
 
 size_t moe_router_smem(int R, int W, bool f32) {
-  return ((size_t)R * W * (f32 ? 4 : 2) + 15) / 16 * 16 + (size_t)kRouterWarps * 2 * R * 4;
+  return ((size_t)R * W * (f32 ? 4 : 2) + 15) / 16 * 16 + (size_t)kRouterWarps * 3 * R * 4;
 }
 cudaError_t moe_router(cudaStream_t s, const float* x, const void* router, const void* corr, bool f32, int R, int W, int top_k,
-                       int32_t* ids, float* wts, int T, int sms) {
+                       int32_t* ids, float* wts, int T, int sms, const RouteOpts& ro) {
   if (T <= 0) return cudaSuccess;
-  if (R <= 0 || top_k <= 0 || top_k > R) return cudaErrorInvalidValue;
+  if (R <= 0 || top_k <= 0 || top_k > R || (ro.groups > 1 && R % ro.groups)) return cudaErrorInvalidValue;
   if (T <= 2 * (sms > 0 ? sms : 148) && R <= 4096) {  // few tokens: a block per token, no staging of the router
-    const size_t sm_small = (size_t)2 * R * 4;
-    if (f32) moe_router_small_kernel<float><<<T, kRouterWarps * 32, sm_small, s>>>(x, (const float*)router, (const float*)corr, R, W, top_k, ids, wts);
-    else moe_router_small_kernel<bf16><<<T, kRouterWarps * 32, sm_small, s>>>(x, (const bf16*)router, (const bf16*)corr, R, W, top_k, ids, wts);
+    const size_t sm_small = (size_t)3 * R * 4;
+    if (f32) moe_router_small_kernel<float><<<T, kRouterWarps * 32, sm_small, s>>>(x, (const float*)router, (const float*)corr, R, W, top_k, ids, wts, ro);
+    else moe_router_small_kernel<bf16><<<T, kRouterWarps * 32, sm_small, s>>>(x, (const bf16*)router, (const bf16*)corr, R, W, top_k, ids, wts, ro);
     return cudaGetLastError();
   }
   const size_t smem = moe_router_smem(R, W, f32);
   if (smem > 200 * 1024) return cudaErrorInvalidValue;
   const int grid = std::max(1, std::min((T + kRouterWarps - 1) / kRouterWarps, sms > 0 ? sms : 148));
-  if (f32) moe_router_kernel<float><<<grid, kRouterWarps * 32, smem, s>>>(x, (const float*)router, (const float*)corr, R, W, top_k, ids, wts, T);
-  else moe_router_kernel<bf16><<<grid, kRouterWarps * 32, smem, s>>>(x, (const bf16*)router, (const bf16*)corr, R, W, top_k, ids, wts, T);
+  if (f32) moe_router_kernel<float><<<grid, kRouterWarps * 32, smem, s>>>(x, (const float*)router, (const float*)corr, R, W, top_k, ids, wts, T, ro);
+  else moe_router_kernel<bf16><<<grid, kRouterWarps * 32, smem, s>>>(x, (const bf16*)router, (const bf16*)corr, R, W, top_k, ids, wts, T, ro);
   return cudaGetLastError();
 }
 
-cudaError_t gated_unit_b16(cudaStream_t s, const bf16* gu, long ldg, int act, bf16* out, int T, int F) {
+cudaError_t gated_unit_b16(cudaStream_t s, const bf16* gu, long ldg, int act, bf16* out, int T, int F, float limit) {
   if (T <= 0) return cudaSuccess;
   if (F % 8 || ldg % 8 || ((uintptr_t)gu & 15) || ((uintptr_t)out & 15)) return cudaErrorInvalidValue;
-  gated_unit_b16_kernel<<<dim3(T, (F / 8 + 255) / 256), 256, 0, s>>>(gu, ldg, act, out, F);
+  gated_unit_b16_kernel<<<dim3(T, (F / 8 + 255) / 256), 256, 0, s>>>(gu, ldg, act, out, F, limit);
   return cudaGetLastError();
 }
 
 cudaError_t moe_expert_rows(cudaStream_t s, const float* x, const bf16* xb, const void* w_gu, const void* w_down, bool f32,
-                            const int32_t* ids, int top_k, int E, int F, int W, float* y, int T, bool packed) {
+                            const int32_t* ids, int top_k, int E, int F, int W, float* y, int T, bool packed, int act, float limit) {
   if (T <= 0) return cudaSuccess;
   const size_t smem = ((size_t)(W + 3) / 4 * 4 + F) * 4;
   if (smem > 200 * 1024) return cudaErrorInvalidValue;
   dim3 grid(T, top_k);
-  if (f32) moe_expert_rows_kernel<float><<<grid, 256, smem, s>>>(x, xb, (const float*)w_gu, (const float*)w_down, ids, E, F, W, y, packed ? 1 : 0);
-  else moe_expert_rows_kernel<bf16><<<grid, 256, smem, s>>>(x, xb, (const bf16*)w_gu, (const bf16*)w_down, ids, E, F, W, y, packed ? 1 : 0);
+  if (f32) moe_expert_rows_kernel<float><<<grid, 256, smem, s>>>(x, xb, (const float*)w_gu, (const float*)w_down, ids, E, F, W, y, packed ? 1 : 0, act, limit);
+  else moe_expert_rows_kernel<bf16><<<grid, 256, smem, s>>>(x, xb, (const bf16*)w_gu, (const bf16*)w_down, ids, E, F, W, y, packed ? 1 : 0, act, limit);
   return cudaGetLastError();
 }
 
 cudaError_t moe_combine(cudaStream_t s, const float* x, const float* y, const int32_t* ids, const float* wts, int top_k, int E, float* out,
-                        int T, int W) {
+                        int T, int W, const float* add) {
   if (T <= 0) return cudaSuccess;
-  moe_combine_kernel<<<T, 256, 0, s>>>(x, y, ids, wts, top_k, E, out, W);
+  moe_combine_kernel<<<T, 256, 0, s>>>(x, y, ids, wts, top_k, E, out, W, add);
   return cudaGetLastError();
 }
 

@@ -66,11 +66,11 @@ __global__ void __launch_bounds__(256) gemm_rt_kernel(const float* __restrict__ 
 // ------------------------------------------------------------------ row kernels
 template <typename WT>
 __global__ void embed_rows_kernel(const int32_t* __restrict__ tokens, const WT* __restrict__ table, float* __restrict__ x,
-                                  bf16* __restrict__ xb, int W) {
+                                  bf16* __restrict__ xb, int W, float scale) {
   const int t = blockIdx.x;
   const WT* src = table + (size_t)tokens[t] * W;
   for (int i = threadIdx.x; i < W; i += blockDim.x) {
-    const float v = ldf<WT>(src, i);
+    const float v = ldf<WT>(src, i) * scale;
     x[(size_t)t * W + i] = v;
     if (xb) xb[(size_t)t * W + i] = __float2bfloat16(v);
   }
@@ -162,9 +162,65 @@ __global__ void __launch_bounds__(256) postnorm_vec_kernel(const float* x, const
   }
 }
 
-__global__ void softcap_kernel(float* __restrict__ z, size_t n, float cap) {
+__global__ void softcap_kernel(float* __restrict__ z, size_t n, float cap, float scale) {
   const size_t stride = (size_t)gridDim.x * blockDim.x;
-  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) z[i] = cap * tanhf(z[i] / cap);
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
+    const float v = z[i] * scale;
+    z[i] = cap > 0.f ? cap * tanhf(v / cap) : v;
+  }
+}
+
+// Element-wise norms N(v) = tanh(alpha v) * w + b (a block [w (W) | b (W) | alpha] of the weight type; no row statistic) around
+// the residual step: v = x[src]; with y: v += post ? N_post(y[r]) : y[r], stored to x_out[r]; with pre: h[r] = N_pre(v) as
+// fp32 and / or bf16.  One launch serves "add the normed output of one sublayer and norm the input of the next".
+// x / x_out are not __restrict__: the step updates the stream in place.
+template <typename WT, int VEC>
+__global__ void __launch_bounds__(256) tanh_norm_kernel(const float* x, const int32_t* __restrict__ row_index, const float* __restrict__ y,
+                                                        long ldy, const WT* __restrict__ post, const WT* __restrict__ pre, float* x_out,
+                                                        float* __restrict__ h, bf16* __restrict__ hb, int W) {
+  const size_t r = blockIdx.y;
+  const size_t src = row_index ? (size_t)row_index[r] : r;
+  const int i0 = (blockIdx.x * blockDim.x + threadIdx.x) * VEC;
+  if (i0 >= W) return;
+  const float a_post = post ? ldf<WT>(post, 2 * (size_t)W) : 0.f, a_pre = pre ? ldf<WT>(pre, 2 * (size_t)W) : 0.f;
+  float v[VEC], hv[VEC];
+  if (VEC == 4) {
+    const float4 t4 = *reinterpret_cast<const float4*>(x + src * W + i0);
+    v[0] = t4.x; v[1] = t4.y; v[2] = t4.z; v[VEC - 1] = t4.w;
+  } else {
+    v[0] = x[src * W + i0];
+  }
+  if (y) {
+    float yv[VEC];
+    if (VEC == 4) {
+      const float4 t4 = *reinterpret_cast<const float4*>(y + r * ldy + i0);
+      yv[0] = t4.x; yv[1] = t4.y; yv[2] = t4.z; yv[VEC - 1] = t4.w;
+    } else {
+      yv[0] = y[r * ldy + i0];
+    }
+#pragma unroll
+    for (int e = 0; e < VEC; ++e)
+      v[e] += post ? fmaf(tanhf(a_post * yv[e]), ldf<WT>(post, i0 + e), ldf<WT>(post, (size_t)W + i0 + e)) : yv[e];
+    if (VEC == 4) *reinterpret_cast<float4*>(x_out + r * W + i0) = make_float4(v[0], v[1], v[2], v[VEC - 1]);
+    else x_out[r * W + i0] = v[0];
+  }
+  if (pre) {
+#pragma unroll
+    for (int e = 0; e < VEC; ++e) hv[e] = fmaf(tanhf(a_pre * v[e]), ldf<WT>(pre, i0 + e), ldf<WT>(pre, (size_t)W + i0 + e));
+    if (VEC == 4) {
+      if (h) *reinterpret_cast<float4*>(h + r * W + i0) = make_float4(hv[0], hv[1], hv[2], hv[VEC - 1]);
+      if (hb) {
+        __nv_bfloat162 lo = __floats2bfloat162_rn(hv[0], hv[1]), hi = __floats2bfloat162_rn(hv[2], hv[VEC - 1]);
+        uint2 pk;
+        pk.x = *reinterpret_cast<unsigned*>(&lo);
+        pk.y = *reinterpret_cast<unsigned*>(&hi);
+        *reinterpret_cast<uint2*>(hb + r * W + i0) = pk;
+      }
+    } else {
+      if (h) h[r * W + i0] = hv[0];
+      if (hb) hb[r * W + i0] = __float2bfloat16(hv[0]);
+    }
+  }
 }
 
 __device__ __forceinline__ float clamped_glu_one(float g, float u, float limit, float act_alpha) {
@@ -741,10 +797,27 @@ cudaError_t gemm_rt(cudaStream_t s, const GemmRtArgs& a) {
   return KERR();
 }
 
-cudaError_t embed_rows_f32(cudaStream_t s, const int32_t* tokens, const void* table, bool f32, float* x, bf16* xb, int T, int W) {
+cudaError_t tanh_norm_step(cudaStream_t s, const float* x, const int32_t* row_index, const float* y, long ldy, const void* post,
+                           const void* pre, bool f32, float* x_out, float* h, bf16* hb, int rows, int W) {
+  if (rows <= 0) return cudaSuccess;
+  if ((y && !x_out) || (!y && !pre)) return cudaErrorInvalidValue;
+  const bool vec = W % 4 == 0 && ldy % 4 == 0 && ((uintptr_t)x & 15) == 0 && ((uintptr_t)y & 15) == 0 && ((uintptr_t)x_out & 15) == 0 &&
+                   ((uintptr_t)h & 15) == 0 && ((uintptr_t)hb & 7) == 0;
+  dim3 grid(((vec ? W / 4 : W) + 255) / 256, rows);
+  if (f32) {
+    if (vec) tanh_norm_kernel<float, 4><<<grid, 256, 0, s>>>(x, row_index, y, ldy, (const float*)post, (const float*)pre, x_out, h, hb, W);
+    else tanh_norm_kernel<float, 1><<<grid, 256, 0, s>>>(x, row_index, y, ldy, (const float*)post, (const float*)pre, x_out, h, hb, W);
+  } else {
+    if (vec) tanh_norm_kernel<bf16, 4><<<grid, 256, 0, s>>>(x, row_index, y, ldy, (const bf16*)post, (const bf16*)pre, x_out, h, hb, W);
+    else tanh_norm_kernel<bf16, 1><<<grid, 256, 0, s>>>(x, row_index, y, ldy, (const bf16*)post, (const bf16*)pre, x_out, h, hb, W);
+  }
+  return cudaGetLastError();
+}
+
+cudaError_t embed_rows_f32(cudaStream_t s, const int32_t* tokens, const void* table, bool f32, float* x, bf16* xb, int T, int W, float scale) {
   if (T <= 0) return cudaSuccess;
-  if (f32) embed_rows_kernel<float><<<T, 128, 0, s>>>(tokens, (const float*)table, x, xb, W);
-  else embed_rows_kernel<bf16><<<T, 128, 0, s>>>(tokens, (const bf16*)table, x, xb, W);
+  if (f32) embed_rows_kernel<float><<<T, 128, 0, s>>>(tokens, (const float*)table, x, xb, W, scale);
+  else embed_rows_kernel<bf16><<<T, 128, 0, s>>>(tokens, (const bf16*)table, x, xb, W, scale);
   return KERR();
 }
 
@@ -783,9 +856,9 @@ cudaError_t norm_rows_f32(cudaStream_t s, const float* x, const int32_t* row_ind
   return postnorm_launch(s, x, row_index, nullptr, 0, nullptr, w, f32, 1.f, off, eps, out, outb, rows, W);
 }
 
-cudaError_t softcap_rows(cudaStream_t s, float* logits, size_t n, float cap) {
-  if (n == 0 || !(cap > 0.f)) return cudaSuccess;
-  softcap_kernel<<<(unsigned)std::min<size_t>((n + 255) / 256, 148 * 16), 256, 0, s>>>(logits, n, cap);
+cudaError_t softcap_rows(cudaStream_t s, float* logits, size_t n, float cap, float scale) {
+  if (n == 0 || (!(cap > 0.f) && scale == 1.f)) return cudaSuccess;
+  softcap_kernel<<<(unsigned)std::min<size_t>((n + 255) / 256, 148 * 16), 256, 0, s>>>(logits, n, cap, scale);
   return KERR();
 }
 

@@ -78,10 +78,15 @@ class ModelDesc:
 MIXER_GLA = 0
 MIXER_LATENT = 1
 MIXER_GQA = 2
+MIXER_DELTA = 3
 MASK_WINDOW, MASK_CHUNK, MASK_CAUSAL = 0, 1, 2
-FF_CLAMPED, FF_GELU_TANH, FF_MOE = 0, 1, 2
-NORM_OF_SUM, NORM_OF_OUTPUT = 0, 1
+FF_CLAMPED, FF_GELU_TANH, FF_MOE, FF_SILU = 0, 1, 2, 3
+NORM_OF_SUM, NORM_OF_OUTPUT, NORM_BOTH_SIDES = 0, 1, 2
+NORM_RMS, NORM_TANH = 0, 1
+ROUTER_SOFTMAX, ROUTER_SIGMOID = 0, 1
+EXPERT_SILU, EXPERT_CLAMPED = 0, 1
 ATTN_QK_UNIT_NORM, ATTN_V_IS_K, ATTN_UNIT_SINK, ATTN_HEAD_GATE = 1, 2, 4, 8
+ATTN_QKV_BIAS, ATTN_QK_PROJ_NORM, ATTN_LEARNED_SINK, ATTN_V_BLEND = 16, 32, 64, 128
 
 
 @dataclass
@@ -115,12 +120,24 @@ class LayerDesc:
     experts: int = 0           # FF_MOE: experts with weights (ff = inner size of one)
     identity_experts: int = 0
     top_k: int = 0
+    score_cap: float = 0.0     # GQA: cap * tanh(s / cap) on the scaled scores; <= 0: off
+    conv_taps: int = 0         # DELTA
+    router_kind: int = ROUTER_SOFTMAX
+    route_groups: int = 0      # FF_MOE: groups of neighbouring experts / groups that stay eligible
+    route_keep: int = 0
+    route_renorm: int = 0      # 1: chosen scores divided by their sum
+    route_scale: float = 0.0   # 0 = 1
+    expert_kind: int = EXPERT_SILU
+    shared_ff: int = 0         # FF_MOE: a unit every token uses
+    shared_limit: float = 0.0
 
     def to_c(self):
         return LayerDescC(self.mixer, self.heads, self.dim, self.vdim, self.tau, self.decay_rank, self.q_rank, self.kv_rank,
                           self.rot_dim, self.rope_dims, self.window, self.kv_from, self.rope_base, self.scale, self.ff, self.ff_limit,
                           self.kv_heads, self.mask, self.attn_flags, self.rope_pairing, self.rope_factor, self.rope_low,
-                          self.rope_high, self.rope_original, self.ff_kind, self.experts, self.identity_experts, self.top_k)
+                          self.rope_high, self.rope_original, self.ff_kind, self.experts, self.identity_experts, self.top_k,
+                          self.score_cap, self.conv_taps, self.router_kind, self.route_groups, self.route_keep, self.route_renorm,
+                          self.route_scale, self.expert_kind, self.shared_ff, self.shared_limit)
 
 
 @dataclass
@@ -136,6 +153,9 @@ class StackDesc:
     norm_place: int = NORM_OF_SUM
     embed_norm: int = 0
     plain_gains: int = 0
+    norm_kind: int = NORM_RMS
+    embed_scale: float = 0.0   # 0 = 1
+    logit_scale: float = 0.0   # 0 = 1
     arch: int = 2
 
     @property
@@ -149,7 +169,8 @@ class StackDesc:
     def to_c(self):
         arr = (LayerDescC * len(self.layers))(*[l.to_c() for l in self.layers])
         return StackDescC(self.width, self.vocab, len(self.layers), self.compute_f32, self.norm_eps, self.resid_alpha,
-                          self.logit_softcap, self.norm_place, self.embed_norm, self.plain_gains), arr
+                          self.logit_softcap, self.norm_place, self.embed_norm, self.plain_gains, self.norm_kind, self.embed_scale,
+                          self.logit_scale), arr
 
 
 @dataclass

@@ -12,7 +12,7 @@ import struct
 import numpy as np
 
 from . import engine as _e
-from .engine import LayerDesc, ModelDesc, StackDesc, bf16_bits, MIXER_GLA, MIXER_LATENT, MIXER_GQA
+from .engine import LayerDesc, ModelDesc, StackDesc, bf16_bits, MIXER_GLA, MIXER_LATENT, MIXER_GQA, MIXER_DELTA
 
 _DT = {"BF16": (np.uint16, 2), "F16": (np.float16, 2), "F32": (np.float32, 4)}
 _IGNORED = ("pooler.", "embeddings.position_ids", "rotary_emb.inv_freq", "cls.", "visual.")  # visual.: the VL tower (not served)
@@ -164,7 +164,58 @@ def lurepel_desc(cfg, shapes=None, compute_f32=False):
                      embed_norm=1, plain_gains=1)
 
 
-STACK_READERS = {"Risepel": risepel_desc, "Lurepel": lurepel_desc}  # layer-list decoders by config.json "architecture"
+def latanex_desc(cfg, shapes=None, compute_f32=False):
+    """config.json of a Latanex checkpoint -> StackDesc: a scaled embedding, tanh norms on both sides of every sublayer,
+    windowed grouped-query attention (biased projections, whole-projection q / k norm, capped scores, learned sinks, values
+    blended with the first blending layer's) and gated-delta-rule layers, silu-gated or mixture-of-experts feed-forwards
+    (sigmoid router, group-limited choice, renormalised and scaled weights, clamped experts, a shared expert).  Every size
+    and every constant that may differ between checkpoints comes from the configuration."""
+    layers = []
+    for i, ly in enumerate(cfg["layers"]):
+        m = ly["mixer"]
+        d = LayerDesc(heads=int(m["heads"]), kv_heads=int(m["kv_heads"]), dim=int(m["dim"]), vdim=int(m["vdim"]))
+        if ly["type"] == "attention":
+            d.mixer, d.scale = MIXER_GQA, float(m["scale"])
+            d.attn_flags = _e.ATTN_QKV_BIAS | _e.ATTN_QK_PROJ_NORM | _e.ATTN_LEARNED_SINK | (_e.ATTN_V_BLEND if m.get("v_mix") else 0)
+            d.score_cap = float(m.get("softcap") or 0.0)
+            mask = m.get("mask")
+            if mask and mask.get("size"):
+                d.mask, d.window = _e.MASK_WINDOW, int(mask["size"])
+            else:
+                d.mask, d.window = _e.MASK_CAUSAL, 0
+        elif ly["type"] == "delta":
+            d.mixer, d.conv_taps = MIXER_DELTA, int(m["conv"])
+        else:
+            raise ValueError(f"layer {i}: unknown layer type {ly['type']!r}")
+        mlp = ly.get("mlp")
+        if mlp is not None:
+            kind = mlp.get("kind")
+            if kind == "dense":
+                d.ff_kind, d.ff = _e.FF_SILU, int(mlp["ff"])
+            elif kind == "moe":
+                r = mlp["router"]
+                d.ff_kind, d.ff, d.ff_limit = _e.FF_MOE, int(mlp["expert"]["ff"]), float(mlp["expert"]["limit"])
+                d.experts, d.top_k = int(r["experts"]), int(r["top"])
+                d.router_kind, d.expert_kind, d.route_renorm = _e.ROUTER_SIGMOID, _e.EXPERT_CLAMPED, 1
+                d.route_scale = float(r.get("scale", 1.0))
+                g = r.get("groups")
+                if g:
+                    d.route_groups, d.route_keep = int(g["count"]), int(g["keep"])
+                sh = mlp.get("shared")
+                if sh:
+                    d.shared_ff, d.shared_limit = int(sh["ff"]), float(sh["limit"])
+            else:
+                raise ValueError(f"layer {i}: unsupported feed-forward kind {kind!r}")
+        layers.append(d)
+    emb = cfg.get("embedding") or {}
+    return StackDesc(width=int(cfg["width"]), vocab=int(cfg["vocab"]), layers=layers, compute_f32=int(bool(compute_f32)),
+                     norm_eps=float(cfg["norm"]["eps"]), resid_alpha=1.0, logit_softcap=0.0, norm_place=_e.NORM_BOTH_SIDES,
+                     norm_kind=_e.NORM_TANH, plain_gains=1, embed_scale=float(emb.get("scale", 1.0)),
+                     logit_scale=float(cfg.get("logit_scale", 1.0)))
+
+
+# layer-list decoders by config.json "architecture"
+STACK_READERS = {"Risepel": risepel_desc, "Lurepel": lurepel_desc, "Latanex": latanex_desc}
 
 
 def desc_from_hf_config(cfg, shapes=None, compute_f32=False):

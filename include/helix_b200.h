@@ -46,7 +46,7 @@
 extern "C" {
 #endif
 
-#define HB_ABI_VERSION 4
+#define HB_ABI_VERSION 5
 
 typedef enum hb_status {
   HB_OK = 0,
@@ -62,8 +62,8 @@ typedef enum hb_arch {
   HB_ARCH_LLAMA = 0,
   HB_ARCH_BERT = 1,
   HB_ARCH_RISEPEL = 2, /* layer-list decoders (hb_stack_desc + hb_layer_desc[]): recurrent, latent-attention and grouped-query
-                          mixers, gated / clamped / mixture-of-experts feed-forwards on a 32-bit residual stream (the Risepel
-                          and Lurepel designs are two settings of it); loaded with hb_model_load_begin_stack */
+                          mixers, gated / clamped / mixture-of-experts feed-forwards on a 32-bit residual stream (the Risepel,
+                          Lurepel and Latanex designs are settings of it); loaded with hb_model_load_begin_stack */
   HB_ARCH_STACK = 2
 } hb_arch;
 
@@ -132,27 +132,58 @@ typedef struct hb_model_desc {
  *                         attn_flags choose: unit-RMS normalisation of rotated q and k, values = the key projection as it
  *                         leaves the matrix product (no value matrix), one unit added to the softmax denominator, a sigmoid
  *                         gate per head from its own projection row.  mask: sliding window, or blocks of `window` positions
- *                         counted from position 0 of the sequence, or plain causal.
- *      Residual step (hb_stack_desc.norm_place): HB_NORM_OF_SUM x <- norm(alpha x + f(x)), or HB_NORM_OF_OUTPUT
- *      x <- x + norm(f(x)); f = mixer and, when ff > 0, the feed-forward (ff_kind):
+ *                         counted from position 0 of the sequence, or plain causal.  Further attn_flags: biases on q / k / v
+ *                         (mix.{q,k,v}.b); unit-RMS normalisation of the WHOLE q (and k) projection with a gain per entry
+ *                         (mix.q.norm, mix.k.norm) instead of per head; a learned sink per head (mix.sink) whose exponential
+ *                         joins the softmax denominator; values blended with the values that the first blending layer of
+ *                         the stack made for the same token, v <- (1 - l) v + l v_first, l = mix.vmix (the blended v is
+ *                         cached; every blending layer has the same kv_heads * vdim).  score_cap > 0: s <- cap tanh(s / cap).
+ *        HB_MIXER_DELTA   gated delta rule: q, k (kv_heads x dim) and v (heads x vdim) pass a causal convolution over
+ *                         conv_taps tokens per channel (mix.{q,k,v}.conv, [channels][taps], last tap = current token) and
+ *                         silu; q and k become unit vectors per head (x / sqrt(sum x^2 + 1e-6)), q times dim^(-1/2);
+ *                         beta = sigmoid(mix.b x), g = exp(-exp(mix.A_log) softplus(mix.a x + mix.dt_bias)) per head;
+ *                         S <- g S; S <- S + k (beta (v - S^T k))^T; o = S^T q; per-head RMS norm of o (gain mix.norm) and
+ *                         silu gate (mix.g).  State slot: S [heads][dim][vdim] fp32 and the last conv_taps - 1 inputs of
+ *                         the three convolutions.
+ *      Residual step (hb_stack_desc.norm_place): HB_NORM_OF_SUM x <- norm(alpha x + f(x)), HB_NORM_OF_OUTPUT
+ *      x <- x + norm(f(x)), or HB_NORM_BOTH_SIDES x <- x + norm_b(f(norm_a(x))) (norm1 / norm1b around the mixer, norm2 /
+ *      norm2b around the feed-forward).  norm_kind: HB_NORM_RMS, or HB_NORM_TANH = tanh(alpha x) * w + b with a scalar
+ *      alpha and a vector b stored beside the gain as <name>.alpha and <name>.b (no statistic of the row; eps unused).
+ *      f = mixer and, when ff > 0, the feed-forward (ff_kind):
  *        HB_FF_CLAMPED    g = min(gate, limit), u = clamp(up, +-limit), y = down(g sigmoid(1.702 g) (u + 1)), with biases
  *        HB_FF_GELU_TANH  y = down(gelu_tanh(gate) * up), no biases
  *        HB_FF_MOE        experts small units down(silu(gate) * up) of inner size ff plus identity_experts outputs that return
  *                         their input; router scores = softmax over all experts + identity outputs in fp32; the top_k largest
  *                         of (score + correction) are chosen and weighted by their scores (not renormalised).
+ *                         Options: router_kind HB_ROUTER_SIGMOID (scores = sigmoid of the logits); route_groups > 1: the
+ *                         experts form that many equal groups of neighbours, a group scores the sum of its two largest
+ *                         corrected scores and only experts of the route_keep best groups can be chosen; route_renorm: the
+ *                         chosen scores are divided by their sum (+ 1e-20); route_scale (0 = 1) multiplies the weights;
+ *                         expert_kind HB_EXPERT_CLAMPED: experts are clamped units (as HB_FF_CLAMPED without biases, limit
+ *                         ff_limit); shared_ff > 0: one more unit of that inner size and kind (limit shared_limit,
+ *                         mlp.shared.*) runs for every token and is added.
+ *        HB_FF_SILU       y = down(silu(gate) * up), no biases
  *      Norm gains are stored as offsets from 1 unless plain_gains.  embed_norm: the embedding row is normed (embed.norm) before
  *      the first layer.  Logits are soft-capped: cap * tanh(z / cap) (cap <= 0: off).  Tensor names: embed[.norm], final.norm,
- *      head, l<i>.norm1/2, l<i>.mix.{q,k,v,g,o,norm,a1,a2,a2.b | dq,dq.norm,uq,dkv,dkv.norm,uk,uv,sink,g,o | q,k,[v,]g,o},
- *      l<i>.mlp.{gate,up,down}[.b] or l<i>.mlp.{router,correction,e<j>.gate,e<j>.up,e<j>.down}. ---- */
-typedef enum hb_mixer { HB_MIXER_GLA = 0, HB_MIXER_LATENT = 1, HB_MIXER_GQA = 2 } hb_mixer;
+ *      head, l<i>.norm1/2[b], l<i>.mix.{q,k,v,g,o,norm,a1,a2,a2.b | dq,dq.norm,uq,dkv,dkv.norm,uk,uv,sink,g,o | q,k,[v,]g,o |
+ *      q,k,v,{q,k,v}.conv,b,a,A_log,dt_bias,norm,g,o}, l<i>.mlp.{gate,up,down}[.b] or
+ *      l<i>.mlp.{router,correction,e<j>.gate,e<j>.up,e<j>.down[,shared.gate,shared.up,shared.down]}. ---- */
+typedef enum hb_mixer { HB_MIXER_GLA = 0, HB_MIXER_LATENT = 1, HB_MIXER_GQA = 2, HB_MIXER_DELTA = 3 } hb_mixer;
 typedef enum hb_mask { HB_MASK_WINDOW = 0, HB_MASK_CHUNK = 1, HB_MASK_CAUSAL = 2 } hb_mask;
-typedef enum hb_ff_kind { HB_FF_CLAMPED = 0, HB_FF_GELU_TANH = 1, HB_FF_MOE = 2 } hb_ff_kind;
-typedef enum hb_norm_place { HB_NORM_OF_SUM = 0, HB_NORM_OF_OUTPUT = 1 } hb_norm_place;
+typedef enum hb_ff_kind { HB_FF_CLAMPED = 0, HB_FF_GELU_TANH = 1, HB_FF_MOE = 2, HB_FF_SILU = 3 } hb_ff_kind;
+typedef enum hb_norm_place { HB_NORM_OF_SUM = 0, HB_NORM_OF_OUTPUT = 1, HB_NORM_BOTH_SIDES = 2 } hb_norm_place;
+typedef enum hb_norm_kind { HB_NORM_RMS = 0, HB_NORM_TANH = 1 } hb_norm_kind;
+typedef enum hb_router_kind { HB_ROUTER_SOFTMAX = 0, HB_ROUTER_SIGMOID = 1 } hb_router_kind;
+typedef enum hb_expert_kind { HB_EXPERT_SILU = 0, HB_EXPERT_CLAMPED = 1 } hb_expert_kind;
 enum {
   HB_ATTN_QK_UNIT_NORM = 1,  /* q and k divided by their root mean square over dim after rotation (no gain) */
   HB_ATTN_V_IS_K = 2,        /* values are the key projections before rotation and normalisation; no mix.v tensor */
   HB_ATTN_UNIT_SINK = 4,     /* p_j = exp(s_j) / (1 + sum exp(s_i)) */
-  HB_ATTN_HEAD_GATE = 8      /* head h's output times sigmoid(row h of mix.g applied to the layer input) */
+  HB_ATTN_HEAD_GATE = 8,     /* head h's output times sigmoid(row h of mix.g applied to the layer input) */
+  HB_ATTN_QKV_BIAS = 16,     /* q, k, v = W x + b (mix.q.b, mix.k.b, mix.v.b) */
+  HB_ATTN_QK_PROJ_NORM = 32, /* q (and k) divided by the root mean square over all heads' entries, times mix.q.norm (mix.k.norm) */
+  HB_ATTN_LEARNED_SINK = 64, /* p_j = exp(s_j) / (exp(sink_h) + sum exp(s_i)), sink_h = mix.sink[h] */
+  HB_ATTN_V_BLEND = 128      /* v <- (1 - l) v + l v_first (mix.vmix; the first such layer of the stack supplies v_first) */
 };
 typedef struct hb_layer_desc {
   int32_t mixer;       /* hb_mixer */
@@ -174,7 +205,16 @@ typedef struct hb_layer_desc {
   int32_t rope_original;                  /* where l < original/high, becomes f/factor where l > original/low, blends between */
   int32_t ff_kind;     /* hb_ff_kind */
   int32_t experts, identity_experts, top_k; /* HB_FF_MOE: experts with weights, outputs that return their input, chosen per token */
-  int32_t reserved[4];
+  float score_cap;     /* GQA: scores pass cap * tanh(s / cap) after the scale; <= 0: off */
+  int32_t conv_taps;   /* DELTA: taps of the causal convolutions (>= 1) */
+  int32_t router_kind; /* hb_router_kind */
+  int32_t route_groups, route_keep; /* HB_FF_MOE: groups of neighbouring experts / groups that stay eligible; <= 1 groups: off */
+  int32_t route_renorm;             /* 1: the chosen scores are divided by their sum */
+  float route_scale;                /* multiplies the weights; 0 = 1 */
+  int32_t expert_kind;              /* hb_expert_kind */
+  int32_t shared_ff;                /* HB_FF_MOE: inner size of the unit every token uses; 0: none */
+  float shared_limit;               /* its clamp (HB_EXPERT_CLAMPED) */
+  int32_t reserved[6];
 } hb_layer_desc;
 typedef struct hb_stack_desc {
   int32_t width, vocab, n_layers;
@@ -183,7 +223,10 @@ typedef struct hb_stack_desc {
   int32_t norm_place;  /* hb_norm_place */
   int32_t embed_norm;  /* 1: x = norm(embed[token]) with gain embed.norm */
   int32_t plain_gains; /* 1: norm gains apply as stored; 0: stored as offsets from one */
-  int32_t reserved[2];
+  int32_t norm_kind;   /* hb_norm_kind of the residual-step, embedding and final norms */
+  float embed_scale;   /* x = embed[token] * embed_scale; 0 = 1 */
+  float logit_scale;   /* logits = head(norm(x)) * logit_scale (before the soft cap); 0 = 1 */
+  int32_t reserved[5];
 } hb_stack_desc;
 
 typedef struct hb_sampling {

@@ -307,3 +307,108 @@ class LatanexOracle:
 def forward(cfg, sd, tokens, trace=None):
     """Whole sequence from position 0 -> logits [T, vocab]."""
     return LatanexOracle(cfg, sd).forward(tokens, taps=trace)
+
+
+# ------------------------------------------------------------------ random checkpoints for tests
+def random_config(width=80, vocab=150, order=(("attention", "dense"), ("delta", "moe"), ("attention", "moe"), ("attention", None)),
+                  heads=6, kv_heads=2, dim=24, vdim=16, window=20, scale=None, softcap=6.0, v_mix=True,
+                  delta=None, ff=72, expert_ff=40, experts=6, groups=(3, 2), top=2, route_scale=1.5, limit=1.5,
+                  shared_ff=48, shared_limit=2.0, embed_scale=2.0, logit_scale=0.5, eps=1e-5, per_layer=None):
+    """A small configuration; `order` lists each layer's (mixer type, feed-forward kind or None); per_layer[i] overrides mixer
+    keys of layer i; delta overrides the delta layers' sizes (heads, kv_heads, dim, vdim, conv)."""
+    dl = dict(heads=4, kv_heads=2, dim=16, vdim=24, conv=4)
+    dl.update(delta or {})
+    layers = []
+    for i, (mix, kind) in enumerate(order):
+        if mix == "attention":
+            mixer = dict(heads=heads, kv_heads=kv_heads, dim=dim, vdim=vdim, scale=float(scale if scale is not None else 2.0 / math.sqrt(dim)),
+                         v_mix=bool(v_mix))
+            if softcap:
+                mixer["softcap"] = float(softcap)
+            if window:
+                mixer["mask"] = dict(size=int(window))
+        else:
+            mixer = dict(dl)
+        mixer.update((per_layer or {}).get(i, {}))
+        if kind == "dense":
+            mlp = dict(kind="dense", ff=ff)
+        elif kind == "moe":
+            router = dict(experts=experts, top=top, scale=float(route_scale))
+            if groups:
+                router["groups"] = dict(count=groups[0], keep=groups[1])
+            mlp = dict(kind="moe", expert=dict(ff=expert_ff, limit=float(limit)), router=router)
+            if shared_ff:
+                mlp["shared"] = dict(ff=shared_ff, limit=float(shared_limit))
+        else:
+            mlp = None
+        layers.append(dict(type=mix, mixer=mixer, mlp=mlp))
+    return dict(architecture="Latanex", width=width, vocab=vocab, layers=layers, norm=dict(eps=eps),
+                embedding=dict(scale=float(embed_scale)), logit_scale=float(logit_scale))
+
+
+def random_state_dict(cfg, seed=0):
+    from .weights import _rng, _t, to_bf16_f32
+    W, V = cfg["width"], cfg["vocab"]
+    s = lambda n: 1.0 / math.sqrt(n)
+    sd = {"embed": _t(seed, "embed", (V, W), 0.5), "head": _t(seed, "head", (V, W), s(W))}
+
+    def norm(name):
+        sd[name] = _t(seed, name, (W,), 0.1, 1.0)
+        sd[name + ".b"] = _t(seed, name + "b", (W,), 0.1)
+        sd[name + ".alpha"] = to_bf16_f32(np.float32(0.4 + 0.4 * _rng(seed, name + "a").random())).reshape(())
+
+    norm("final.norm")
+    for i, ly in enumerate(cfg["layers"]):
+        m, p = ly["mixer"], f"l{i}."
+        H, G, D, Dv = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
+        norm(p + "norm1")
+        norm(p + "norm1b")
+        if ly["type"] == "attention":
+            sd[p + "mix.q"] = _t(seed, p + "q", (H * D, W), s(W))
+            sd[p + "mix.k"] = _t(seed, p + "k", (G * D, W), s(W))
+            sd[p + "mix.v"] = _t(seed, p + "v", (G * Dv, W), s(W))
+            for n, rows in (("q", H * D), ("k", G * D), ("v", G * Dv)):
+                sd[p + f"mix.{n}.b"] = _t(seed, p + n + "b", (rows,), 0.2)
+            sd[p + "mix.q.norm"] = _t(seed, p + "qn", (H * D,), 0.2, 1.0)
+            sd[p + "mix.k.norm"] = _t(seed, p + "kn", (G * D,), 0.2, 1.0)
+            sd[p + "mix.vmix"] = to_bf16_f32(np.float32(0.2 + 0.5 * _rng(seed, p + "vm").random())).reshape(())
+            sd[p + "mix.sink"] = _t(seed, p + "sink", (H,), 1.0)
+            sd[p + "mix.o"] = _t(seed, p + "o", (W, H * Dv), s(H * Dv))
+        else:
+            taps = m["conv"]
+            sd[p + "mix.q"] = _t(seed, p + "q", (G * D, W), 2.0 * s(W))
+            sd[p + "mix.k"] = _t(seed, p + "k", (G * D, W), 2.0 * s(W))
+            sd[p + "mix.v"] = _t(seed, p + "v", (H * Dv, W), 2.0 * s(W))
+            for n, rows in (("q", G * D), ("k", G * D), ("v", H * Dv)):
+                sd[p + f"mix.{n}.conv"] = _t(seed, p + n + "c", (rows, taps), 0.6)
+            sd[p + "mix.b"] = _t(seed, p + "b", (H, W), 2.0 * s(W))
+            sd[p + "mix.a"] = _t(seed, p + "a", (H, W), 2.0 * s(W))
+            sd[p + "mix.A_log"] = _t(seed, p + "A", (H,), 0.5, -1.5)
+            sd[p + "mix.dt_bias"] = _t(seed, p + "dt", (H,), 0.5)
+            sd[p + "mix.norm"] = _t(seed, p + "hn", (Dv,), 0.1, 1.0)
+            sd[p + "mix.g"] = _t(seed, p + "g", (H * Dv, W), 2.0 * s(W))
+            sd[p + "mix.o"] = _t(seed, p + "o", (W, H * Dv), s(H * Dv))
+        mlp = ly.get("mlp")
+        if not mlp:
+            continue
+        norm(p + "norm2")
+        norm(p + "norm2b")
+
+        def unit(pre, Fn):
+            sd[pre + "gate"] = _t(seed, pre + "g", (Fn, W), 2.0 * s(W))
+            sd[pre + "up"] = _t(seed, pre + "u", (Fn, W), 2.0 * s(W))
+            sd[pre + "down"] = _t(seed, pre + "d", (W, Fn), s(Fn))
+
+        if mlp["kind"] == "dense":
+            unit(p + "mlp.", mlp["ff"])
+        else:
+            r = mlp["router"]
+            E = r["experts"]
+            sd[p + "mlp.router"] = _t(seed, p + "router", (E, W), 3.0 * s(W))
+            # choice corrections on a shuffled grid: no two experts tie by their corrections alone
+            sd[p + "mlp.correction"] = to_bf16_f32((_rng(seed, p + "corr").permutation(E) - (E - 1) / 2.0) * 0.0625)
+            for e in range(E):
+                unit(p + f"mlp.e{e}.", mlp["expert"]["ff"])
+            if mlp.get("shared"):
+                unit(p + "mlp.shared.", mlp["shared"]["ff"])
+    return sd

@@ -411,13 +411,14 @@ static size_t carve_stack(Model* m, const hb_stack_desc& d, const hb_layer_desc*
         put(p + "mix.sink", sk, 0, H, 1, false, 1.f, true);
       }
       if (l.attn_flags & HB_ATTN_V_BLEND) {
-        uint8_t* vm = take(1);
-        w.vmix = vm;
-        put(p + "mix.vmix", vm, 0, 1, 1, false, 1.f, true);
-        w.blend_role = 2;
         bool earlier = false;
         for (int j = 0; j < i; ++j) earlier |= L[j].mixer == HB_MIXER_GQA && (L[j].attn_flags & HB_ATTN_V_BLEND);
-        if (!earlier) w.blend_role = 1;
+        w.blend_role = earlier ? 2 : 1;
+        if (earlier) {  // the first blending layer keeps its own values: it has no use for a blend weight
+          uint8_t* vm = take(1);
+          w.vmix = vm;
+          put(p + "mix.vmix", vm, 0, 1, 1, false, 1.f, true);
+        }
       }
       uint8_t* o = take(W * H * Dv);
       put(p + "mix.o", o, 0, W, H * Dv);

@@ -157,6 +157,7 @@ class StackDesc:
     embed_scale: float = 0.0   # 0 = 1
     logit_scale: float = 0.0   # 0 = 1
     arch: int = 2
+    unused_tensors: frozenset = frozenset()  # checkpoint tensors the design names but this stack has no use for (skipped at load)
 
     @property
     def hidden(self):
@@ -284,6 +285,8 @@ class Engine:
         """tensors: {HF checkpoint name: fp32/bf16-representable ndarray}."""
         self.load_begin(desc)
         for name, a in tensors.items():
+            if name in getattr(desc, "unused_tensors", ()):
+                continue
             bits = bf16_bits(a)
             self._ck(self._l.hb_model_tensor_set(self._h, name.encode(), bits.ctypes.data, bits.size))
         self._ck(self._l.hb_model_load_finish(self._h))

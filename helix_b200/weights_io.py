@@ -75,6 +75,8 @@ def load_safetensors(engine, desc: ModelDesc, paths):
                 continue
             if getattr(desc, "tie_embeddings", 0) and cname == "lm_head.weight":
                 continue
+            if cname in getattr(desc, "unused_tensors", ()):
+                continue
             bits = to_bf16_bits(dt, arr)
             engine._ck(l.hb_model_tensor_set(h, cname.encode(), bits.ctypes.data, bits.size))
     engine._ck(l.hb_model_load_finish(h))
@@ -208,7 +210,14 @@ def latanex_desc(cfg, shapes=None, compute_f32=False):
                 raise ValueError(f"layer {i}: unsupported feed-forward kind {kind!r}")
         layers.append(d)
     emb = cfg.get("embedding") or {}
-    return StackDesc(width=int(cfg["width"]), vocab=int(cfg["vocab"]), layers=layers, compute_f32=int(bool(compute_f32)),
+    # a checkpoint may carry a blend weight for every attention layer; only layers that blend with an earlier one use theirs
+    seen, unused = False, set()
+    for i, d in enumerate(layers):
+        if d.mixer == MIXER_GQA:
+            if not (d.attn_flags & _e.ATTN_V_BLEND) or not seen:
+                unused.add(f"l{i}.mix.vmix")
+            seen = seen or bool(d.attn_flags & _e.ATTN_V_BLEND)
+    return StackDesc(unused_tensors=frozenset(unused), width=int(cfg["width"]), vocab=int(cfg["vocab"]), layers=layers, compute_f32=int(bool(compute_f32)),
                      norm_eps=float(cfg["norm"]["eps"]), resid_alpha=1.0, logit_softcap=0.0, norm_place=_e.NORM_BOTH_SIDES,
                      norm_kind=_e.NORM_TANH, plain_gains=1, embed_scale=float(emb.get("scale", 1.0)),
                      logit_scale=float(cfg.get("logit_scale", 1.0)))

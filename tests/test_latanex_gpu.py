@@ -225,6 +225,7 @@ def test_first_tokens_and_the_sink():
     def no_sink(desc):
         for l in desc.layers:
             l.attn_flags &= ~ATTN_LEARNED_SINK
+    sd.pop("l0.mix.sink")
     with make_engine(cfg, sd, 1, edit=no_sink) as e:  # the flag is a parameter of the mechanism
         assert row_err(replay(e, toks, [7, 2]), bare).max() < TOL[1]
 

@@ -16,7 +16,7 @@ cache.  tokens = sessions * (seq + decode).
                  oracle port on all host threads (pinned with threadpoolctl), bounded sample; --cpu-impl hf switches to
                  HF transformers on torch CPU, which measured 30x slower on the GPU box (profiles/r02c_reference_hf.json)
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--workload llama8b|bge|pack|risepel|lurepel]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--workload llama8b|bge|pack|risepel|lurepel|latanex]
 """
 import argparse
 import json
@@ -396,9 +396,13 @@ def bench_lurepel(args):
     return bench_stack(args, "lurepel")
 
 
+def bench_latanex(args):
+    return bench_stack(args, "latanex")
+
+
 def bench_stack(args, family):
-    """--workload risepel | lurepel: prefill and decode throughput of layer-list decoder stacks of that design
-    (helix_b200.configs.risepel_stack / lurepel_stack, random
+    """--workload risepel | lurepel | latanex: prefill and decode throughput of layer-list decoder stacks of that design
+    (helix_b200.configs.risepel_stack / lurepel_stack / latanex_stack, random
     weights, bf16 serving mode) at a few layer sizes, beside a Llama-family model of equal width / depth / feed-forward size
     through the same engine API.  Per size: `sessions` prompts of `seq` tokens + `decode` generated tokens each; tokens/s =
     tokens / device time of the forward passes of each phase; `families` = CUDA-event spans of one profiled pass by kernel
@@ -414,7 +418,7 @@ def bench_stack(args, family):
     for width, layers in sizes:
         ff = 4 * width
         row = {"width": width, "layers": layers, "ff": ff}
-        build = {"risepel": configs.risepel_stack, "lurepel": configs.lurepel_stack}[family]
+        build = {"risepel": configs.risepel_stack, "lurepel": configs.lurepel_stack, "latanex": configs.latanex_stack}[family]
         for name, desc in ((family, build(width, layers, ff=ff)), ("llama", configs.llama_like(width, layers, ff))):
             e = hb.Engine(hb.EngineConfig(device=0, max_seqs=sessions, max_ctx=seq + decode + 64,
                                           max_batched_tokens=args.max_batched_tokens, use_cuda_graphs=0 if args.no_graphs else 1))
@@ -437,7 +441,7 @@ def bench_stack(args, family):
             fam = {}
             for i, (label, unit) in enumerate((("gemm_tcgen05_prefill", "TFLOP/s"), ("attention_prefill", "TFLOP/s"), ("attention_decode", "GB/s"),
                                                ("row_kernels", "GB/s"), ("gemm_decode", "GB/s"), ("gemm_cuda_core", "TFLOP/s"),
-                                               ("gla_recurrence", "TFLOP/s"), ("stack_attention", "TFLOP/s"))):
+                                               ("recurrence", "TFLOP/s"), ("stack_attention", "TFLOP/s"))):
                 ms = p1["prof_ms"][i] - p0["prof_ms"][i]
                 if ms <= 0:
                     continue
@@ -586,8 +590,8 @@ def main():
     ap.add_argument("--mixed-step-tokens", type=int, default=512)
     ap.add_argument("--fixed-total-sessions", type=int, default=256)
     ap.add_argument("--layers", type=int, default=0, help="debug: truncate the model (INVALID as a bench number)")
-    ap.add_argument("--workload", default="llama8b", choices=["llama8b", "bge", "pack", "risepel", "lurepel"])
-    ap.add_argument("--risepel-sizes", nargs="*", default=[], help="risepel / lurepel workloads: WIDTHxLAYERS ... (default 1024x12 2048x12 4096x6)")
+    ap.add_argument("--workload", default="llama8b", choices=["llama8b", "bge", "pack", "risepel", "lurepel", "latanex"])
+    ap.add_argument("--risepel-sizes", nargs="*", default=[], help="risepel / lurepel / latanex workloads: WIDTHxLAYERS ... (default 1024x12 2048x12 4096x6)")
     ap.add_argument("--chunks", type=int, default=100000)
     ap.add_argument("--ragged", action="store_true", help="bge workload: chunk lengths U[64,512] instead of 512")
     ap.add_argument("--pack-seconds", type=float, default=8.0)
@@ -601,9 +605,9 @@ def main():
     if args.impl == "reference":
         reference_arm(args, rank, world)
         return
-    if args.workload in ("bge", "pack", "risepel", "lurepel"):
+    if args.workload in ("bge", "pack", "risepel", "lurepel", "latanex"):
         if rank == 0:
-            {"bge": bench_bge, "pack": bench_pack, "risepel": bench_risepel, "lurepel": bench_lurepel}[args.workload](args)
+            {"bge": bench_bge, "pack": bench_pack, "risepel": bench_risepel, "lurepel": bench_lurepel, "latanex": bench_latanex}[args.workload](args)
         return
 
     import torch

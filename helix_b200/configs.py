@@ -97,6 +97,36 @@ def lurepel_stack(width, layers, ff=None, chunk=1024, experts=16, identity=1, to
                        logit_softcap=0.0, norm_place=E.NORM_OF_OUTPUT, embed_norm=1, plain_gains=1)
 
 
+def latanex_stack(width, layers, ff=None, window=1024, experts=16, top=4, groups=(4, 2), vocab=32768, compute_f32=False):
+    """A Latanex-design stack at sizes that resemble a served model's layers (random-init benchmarks): heads of 128 channels,
+    four query heads per key/value head, a sliding window, capped scores, learned sinks and blended values; every fourth
+    layer (the third of each four) is a gated-delta-rule layer with 128 x 128 states and four-tap convolutions; the first
+    layer has a dense gated feed-forward of size ff, the others a mixture of `experts` clamped experts of size 3 ff / 16 of
+    which every token uses `top` out of the best groups, plus a shared expert of size ff / 4: the products of a dense unit of
+    size ff per token."""
+    from . import engine as E
+    heads = max(1, width // 128)
+    ff = ff or (width * 4)
+    flags = E.ATTN_QKV_BIAS | E.ATTN_QK_PROJ_NORM | E.ATTN_LEARNED_SINK | E.ATTN_V_BLEND
+    out = []
+    for i in range(layers):
+        if i % 4 == 2:
+            l = E.LayerDesc(mixer=E.MIXER_DELTA, heads=heads, kv_heads=max(1, heads // 2), dim=128, vdim=128, conv_taps=4)
+        else:
+            l = E.LayerDesc(mixer=E.MIXER_GQA, heads=heads, kv_heads=max(1, heads // 4), dim=128, vdim=128, scale=128 ** -0.5,
+                            attn_flags=flags, mask=E.MASK_WINDOW, window=window, score_cap=30.0)
+        if i == 0:
+            l.ff_kind, l.ff = E.FF_SILU, ff
+        else:
+            l.ff_kind, l.ff, l.ff_limit, l.experts, l.top_k = E.FF_MOE, max(64, 3 * ff // 16), 7.0, experts, top
+            l.router_kind, l.expert_kind, l.route_renorm, l.route_scale = E.ROUTER_SIGMOID, E.EXPERT_CLAMPED, 1, 2.5
+            l.route_groups, l.route_keep = groups
+            l.shared_ff, l.shared_limit = max(64, ff // 4), 7.0
+        out.append(l)
+    return E.StackDesc(width=width, vocab=vocab, layers=out, compute_f32=int(compute_f32), norm_eps=1e-5, resid_alpha=1.0,
+                       norm_place=E.NORM_BOTH_SIDES, norm_kind=E.NORM_TANH, plain_gains=1, embed_scale=1.0, logit_scale=0.25)
+
+
 def llama_like(width, layers, ff, vocab=32768):
     """The closest existing decoder at equal width / depth / feed-forward size (comparison arm of the layer-list benchmarks)."""
     heads = max(1, width // 128)

@@ -60,7 +60,8 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_const
                    float scale_log2, bf16* __restrict__ out_direct, int ldo, const int* sig_wait, int sig_wait_count,
                    int* sig_done, int bank_tiles, const bf16* __restrict__ k_cache, const bf16* __restrict__ v_cache,
                    unsigned long long* trace, const int* dep_wait, int dep_count, int* dep_done,
-                   const __grid_constant__ DecodeRope rope, int chunk, int sink, const float* __restrict__ head_gate, int ldg) {
+                   const __grid_constant__ DecodeRope rope, int chunk, int sink, const float* __restrict__ head_gate, int ldg,
+                   int window, float cap_in, float cap_out, const bf16* __restrict__ sink_w) {
   using C = DCfg<D>;
   constexpr int STAGES = C::STAGES;
   extern __shared__ uint8_t smem_raw[];
@@ -95,7 +96,8 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_const
   const int n_tiles_total = (ctx + BKV - 1) / BKV;
   // block mask (chunk > 0): the new position sees only its own block of `chunk` positions, counted from position 0; the
   // splits share the tiles from the one that holds the block start
-  const int kv_lo = chunk > 0 ? (ctx - 1) / chunk * chunk : 0;
+  // sliding window (window > 0): the last `window` positions
+  const int kv_lo = chunk > 0 ? (ctx - 1) / chunk * chunk : (window > 0 ? max(0, ctx - window) : 0);
   const int t_first = kv_lo / BKV;
   const int tps = (n_tiles_total - t_first + num_splits - 1) / num_splits;
   const int t_begin = t_first + split * tps;
@@ -348,7 +350,10 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_const
       float sc[G], mx[G];
 #pragma unroll
       for (int g = 0; g < G; ++g) {
-        sc[g] = valid ? __uint_as_float(sv[g]) * scale_log2 : -INFINITY;
+        float sg = __uint_as_float(sv[g]) * scale_log2;
+        if (cap_in > 0.f)  // capped scores: cap tanh(scale s / cap) in the exp2 domain, tanh(y) = 1 - 2 / (e^2y + 1)
+          sg = fmaf(-2.f * cap_out, __fdividef(1.f, fast_exp2(__uint_as_float(sv[g]) * cap_in) + 1.f), cap_out);
+        sc[g] = valid ? sg : -INFINITY;
         mx[g] = sc[g];
       }
 #pragma unroll
@@ -428,6 +433,7 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_const
         for (int g = 0; g < G; ++g) {
           float lg = redl[g] + redl[kMaxG + g] + redl[2 * kMaxG + g] + redl[3 * kMaxG + g];
           if (sink) lg += fast_exp2(-m_used[g]);  // one more unit in the denominator: a key of score 0 without a value
+          if (sink_w != nullptr) lg += fast_exp2(__bfloat162float(sink_w[kvh * G + g]) * 1.4426950408889634f - m_used[g]);
           float gl = 1.f;
           if (head_gate != nullptr) gl = 1.f / (1.f + __expf(-head_gate[(size_t)b * ldg + kvh * G + g]));
           out_direct[(size_t)b * ldo + (size_t)(kvh * G + g) * D + t] =
@@ -462,7 +468,7 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_const
 template <int D>
 __global__ void __launch_bounds__(D / 2)
 attn_decode_combine_kernel(const float* __restrict__ ws, bf16* __restrict__ out, int ldo, int Hq, int Hkv, int G,
-                           int num_splits, int sink, const float* __restrict__ head_gate, int ldg) {
+                           int num_splits, int sink, const float* __restrict__ head_gate, int ldg, const bf16* __restrict__ sink_w) {
   pdl_launch_dependents();
   pdl_wait();
   const int h = blockIdx.x, b = blockIdx.y;
@@ -483,6 +489,7 @@ attn_decode_combine_kernel(const float* __restrict__ ws, bf16* __restrict__ out,
     o1 += w * p[d + 1];
   }
   if (sink && m != -INFINITY) l += fast_exp2(-m);
+  if (sink_w != nullptr && m != -INFINITY) l += fast_exp2(__bfloat162float(sink_w[h]) * 1.4426950408889634f - m);
   float inv = l > 0.f ? 1.0f / l : 0.f;
   if (head_gate != nullptr) inv *= 1.f / (1.f + __expf(-head_gate[(size_t)b * ldg + h]));
   *reinterpret_cast<__nv_bfloat162*>(out + (size_t)b * ldo + h * D + d) = __floats2bfloat162_rn(o0 * inv, o1 * inv);
@@ -507,10 +514,12 @@ cudaError_t launch(cudaStream_t stream, const AttnDecodeArgs& a) {
                            a.page_table, a.max_pages, a.ctx_lens, a.workspace, a.Hkv, a.num_splits,
                            a.scale * 1.4426950408889634f, direct, a.ldo, a.sig.wait, a.sig.wait_count, a.sig.done, bank_tiles,
                            a.k_cache, a.v_cache, a.sig.trace, a.sig.dep.wait, a.sig.dep.wait_count, a.sig.dep.done,
-                           a.num_splits == 1 ? a.rope : DecodeRope{}, a.block_mask, a.unit_sink, a.head_gate, a.ldg);
+                           a.num_splits == 1 ? a.rope : DecodeRope{}, a.block_mask, a.unit_sink, a.head_gate, a.ldg, a.window,
+                           a.softcap > 0.f ? 2.f * 1.4426950408889634f * a.scale / a.softcap : 0.f,
+                           a.softcap > 0.f ? a.softcap * 1.4426950408889634f : 0.f, a.sink);
   if (e != cudaSuccess || direct) return e;
   return launch_k(attn_decode_combine_kernel<D>, dim3(a.Hq, a.B), dim3(D / 2), 0, stream, true,
-                  (const float*)a.workspace, a.out, a.ldo, a.Hq, a.Hkv, G, a.num_splits, a.unit_sink, a.head_gate, a.ldg);
+                  (const float*)a.workspace, a.out, a.ldo, a.Hq, a.Hkv, G, a.num_splits, a.unit_sink, a.head_gate, a.ldg, a.sink);
 }
 
 }  // namespace
@@ -537,7 +546,8 @@ size_t attn_decode_workspace_floats(int B, int Hq, int D, int num_splits) {
 
 cudaError_t attn_decode(cudaStream_t stream, const AttnDecodeArgs& a) {
   if (a.B <= 0) return cudaSuccess;
-  if (a.page_size != PAGE || a.Hq % a.Hkv || a.num_splits < 1 || a.num_pages <= 0 || a.block_mask < 0) return cudaErrorInvalidValue;
+  if (a.page_size != PAGE || a.Hq % a.Hkv || a.num_splits < 1 || a.num_pages <= 0 || a.block_mask < 0 || a.window < 0 ||
+      (a.window > 0 && a.block_mask > 0)) return cudaErrorInvalidValue;
   const int G = a.Hq / a.Hkv;
   if (a.D == 128) {
     switch (G) {

@@ -108,7 +108,8 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
                     bf16* __restrict__ out, int ldo,
                     const int32_t* __restrict__ cu_seqlens, int B, int Hq, int group, int causal, float scale_log2,
                     int max_q_pairs, const int32_t* __restrict__ kv_lens, const int32_t* __restrict__ page_table,
-                    int max_pages, int Hkv, int chunk, int sink, const float* __restrict__ head_gate, int ldg) {
+                    int max_pages, int Hkv, int chunk, int sink, const float* __restrict__ head_gate, int ldg,
+                    int window, float cap_in, float cap_out, const bf16* __restrict__ sink_w) {
   using C = ACfg<D>;
   constexpr int KST = C::STAGES;
   extern __shared__ uint8_t smem_raw[];
@@ -158,7 +159,10 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     // causal: q tile t needs kv tiles up to the one holding its last row's own position
     // block mask (chunk > 0, paged only): a row sees its own block of `chunk` positions, counted from position 0, up to
     // itself; tiles before the block of the pair's first row are skipped, n0 / n1 / n count tiles from j_lo
-    it.j_lo = (PAGED && chunk > 0) ? ((it.q_off + it.q0) / chunk * chunk) / BKV : 0;
+    // sliding window (window > 0, paged only): a row sees the `window` positions that end with itself; tiles before the
+    // window of the pair's first row are skipped
+    it.j_lo = (PAGED && chunk > 0) ? ((it.q_off + it.q0) / chunk * chunk) / BKV
+              : (PAGED && window > 0) ? max(0, it.q_off + it.q0 - window + 1) / BKV : 0;
     it.n0 = (causal ? min(kv_tiles, (it.q_off + it.q0 + BQ - 1) / BKV + 1) : kv_tiles) - it.j_lo;
     it.n1 = it.act1 ? (causal ? min(kv_tiles, (it.q_off + it.q0 + 2 * BQ - 1) / BKV + 1) : kv_tiles) - it.j_lo : 0;
     it.n = max(it.n0, it.n1);
@@ -376,9 +380,9 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
         tc_fence_after();
         if (t == 0 && warp == 3 && lane == 0) HB_TRACE(3);  // got S0(j)
         const int kv0 = (it.j_lo + j) * BKV;
-        const int lo = chunk > 0 ? qpos / chunk * chunk : 0;     // first kv position this row sees
+        const int lo = chunk > 0 ? qpos / chunk * chunk : (window > 0 ? qpos - window + 1 : 0);  // first kv position this row sees
         const bool need_mask = (kv0 + BKV > len) || (causal && (kv0 + BKV - 1 > qt0)) ||
-                               (chunk > 0 && kv0 < (qt0 + BQ - 1) / chunk * chunk);
+                               (chunk > 0 && kv0 < (qt0 + BQ - 1) / chunk * chunk) || (window > 0 && kv0 < qt0 + BQ - window);
         const int lim = causal ? min(len - 1, qpos) : len - 1;  // last valid kv position for this row
         // ---- the S row: back-to-back TMEM loads, ONE wait, then max / exp2 / pack entirely in registers
         uint32_t sv[BKV];
@@ -388,6 +392,15 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
           tmem_ld_32x32b_x32(tS + c * 32, dst);
         }
         tmem_ld_wait();
+        if (cap_in > 0.f) {
+          // capped scores: s <- cap tanh(scale s / cap), left in the exp2 domain (cap_out = cap log2 e); tanh(y) = 1 - 2 / (e^2y + 1)
+          // with cap_in = 2 log2(e) scale / cap.  The scale below is then one.
+#pragma unroll
+          for (int i = 0; i < BKV; ++i) {
+            const float e2 = fast_exp2(__uint_as_float(sv[i]) * cap_in);
+            sv[i] = __float_as_uint(fmaf(-2.f * cap_out, __fdividef(1.f, e2 + 1.f), cap_out));
+          }
+        }
         if (need_mask) {  // diagonal / ragged tiles only: knock the invalid columns out once, the hot loops stay branch-free
 #pragma unroll
           for (int i = 0; i < BKV; ++i) sv[i] = (kv0 + i <= lim && kv0 + i >= lo) ? sv[i] : 0xff800000u;  // -inf
@@ -398,7 +411,8 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
 #pragma unroll
         for (int i = 8; i < BKV; ++i) mx8[i & 7] = fmaxf(mx8[i & 7], __uint_as_float(sv[i]));
         const float mx = fmaxf(fmaxf(fmaxf(mx8[0], mx8[1]), fmaxf(mx8[2], mx8[3])), fmaxf(fmaxf(mx8[4], mx8[5]), fmaxf(mx8[6], mx8[7])));
-        float m_new = (mx == -INFINITY) ? m_used : mx * scale_log2;
+        const float sl2 = cap_in > 0.f ? 1.f : scale_log2;
+        float m_new = (mx == -INFINITY) ? m_used : mx * sl2;
         if (j == 0) {
           m_used = m_new;
         } else {
@@ -425,7 +439,7 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
         // ---- p = exp2(s*scale - m) (masked entries are -inf -> 0), row sum, P (bf16x2) written over the S buffer's head.
         //      POLY of every 8 column pairs take the FMA-pipe exp2, the rest the SFU; scale/subtract and the sum are packed
         if (t == 0 && warp == 3 && lane == 0) HB_TRACE(4);  // loaded, max, rescale decision done
-        const uint64_t scale2 = f2_pack(scale_log2, scale_log2), negm2 = f2_pack(-m_used, -m_used);
+        const uint64_t scale2 = f2_pack(sl2, sl2), negm2 = f2_pack(-m_used, -m_used);
         uint64_t sum2a = 0, sum2b = 0;
 #pragma unroll
         for (int c = 0; c < BKV / 16; ++c) {
@@ -465,6 +479,7 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
       mbar_wait(&pv_done[t * 2 + ((jt + nt - 1) & 1)], ((jt + nt - 1) >> 1) & 1);
       tc_fence_after();
       if (sink) l += fast_exp2(-m_used);  // one more unit in the denominator: a key of score 0 that carries no value
+      if (sink_w != nullptr) l += fast_exp2(__bfloat162float(sink_w[it.h]) * 1.4426950408889634f - m_used);  // a learned one per head
       float inv_l = l > 0.f ? 1.0f / l : 0.f;
       // optional output gate: the head's rows are scaled by sigmoid(head_gate[token][head]) on their way out
       if (head_gate != nullptr && qrow < it.len) inv_l *= 1.f / (1.f + __expf(-head_gate[(size_t)(it.seq0 + qrow) * ldg + it.h]));
@@ -574,7 +589,9 @@ cudaError_t launch_p(cudaStream_t stream, const AttnPrefillArgs& a) {
   const float scale_log2 = a.scale * 1.4426950408889634f;
   kern<<<grid, kThreads, C::SMEM, stream>>>(mq, mk, mv, mo, a.out, a.ldo, a.cu_seqlens, a.B, a.Hq, a.Hq / a.Hkv, a.causal,
                                             scale_log2, max_q_pairs, a.kv_lens, a.page_table, a.max_pages, a.Hkv,
-                                            paged_only(a.block_mask, PAGED), a.unit_sink, a.head_gate, a.ldg);
+                                            paged_only(a.block_mask, PAGED), a.unit_sink, a.head_gate, a.ldg,
+                                            paged_only(a.window, PAGED), a.softcap > 0.f ? 2.f * 1.4426950408889634f * a.scale / a.softcap : 0.f,
+                                            a.softcap > 0.f ? a.softcap * 1.4426950408889634f : 0.f, a.sink);
   return cudaGetLastError();
 }
 
@@ -647,6 +664,7 @@ cudaError_t attn_prefill(cudaStream_t stream, const AttnPrefillArgs& a) {
   const bool paged = a.k_cache != nullptr;
   if ((a.ldq % 8) || (a.ldo % 8) || (!paged && ((a.ldk % 8) || (a.ldv % 8)))) return cudaErrorInvalidValue;
   if (a.block_mask < 0 || (a.block_mask > 0 && (!paged || !a.causal))) return cudaErrorInvalidValue;
+  if (a.window < 0 || (a.window > 0 && (!paged || !a.causal || a.block_mask > 0))) return cudaErrorInvalidValue;
   if (paged) {
     if (!a.v_cache || !a.page_table || !a.kv_lens || a.max_pages <= 0 || a.num_pages <= 0 || a.page_size != 64) return cudaErrorInvalidValue;
     if (a.D == 128) return launch<128, true>(stream, a);

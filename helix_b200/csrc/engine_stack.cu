@@ -575,8 +575,10 @@ int Engine::forward_stack(int T, int B, const StepLayout& L, const int32_t* extr
   auto gated_ff = [&](const void* w_gu, const void* w_down, int F, int act, float limit, bool packed, float* out) -> int {
     int rc;
     if (T > 256 && k.gu16 && F % 8 == 0 && stack_tc(2 * F, W, W, W) && stack_tc(W, F, F, W)) {
-      if (packed && act != GLU_CLAMPED) {
-        GemmArgs g{x16, W, (const bf16*)w_gu, W, mo16, F, nullptr, 0, nullptr, T, 2 * F, W, act == GLU_GELU_TANH ? EPI_GEGLU : EPI_SWIGLU, 0};
+      if (packed) {
+        GemmArgs g{x16, W, (const bf16*)w_gu, W, mo16, F, nullptr, 0, nullptr, T, 2 * F, W,
+                   act == GLU_GELU_TANH ? EPI_GEGLU : (act == GLU_CLAMPED ? EPI_CLAMPGLU : EPI_SWIGLU), 0};
+        g.glu_limit = limit;
         SPAN(0, 4.0 * T * F * W, gemm_bf16_tn(stream_, g));
       } else {
         GemmArgs g{x16, W, (const bf16*)w_gu, W, k.gu16, 2 * F, nullptr, 0, nullptr, T, 2 * F, W, EPI_NONE, 0};
@@ -826,7 +828,7 @@ int Engine::forward_stack(int T, int B, const StepLayout& L, const int32_t* extr
       const int eact = l.expert_kind == HB_EXPERT_CLAMPED ? GLU_CLAMPED : GLU_SILU;
       const float* add = nullptr;
       if (l.shared_ff > 0) {  // the unit every token uses; the combination below starts from its output
-        rc = gated_ff(w.w_gu_sh, w.w_down_sh, l.shared_ff, eact, l.shared_limit, false, k.y2);
+        rc = gated_ff(w.w_gu_sh, w.w_down_sh, l.shared_ff, eact, l.shared_limit, w.sh_packed, k.y2);
         if (rc != HB_OK) return rc;
         add = k.y2;
       }
@@ -852,8 +854,9 @@ int Engine::forward_stack(int T, int B, const StepLayout& L, const int32_t* extr
         if (items > 4096) launches_.fetch_add(2, std::memory_order_relaxed);  // three kernels behind one call
         SPAN(3, 4.0 * rows * W, moe_gather_rows(stream_, x16, W, k.moe_src, k.moe_a16, rows));
         if (w.gu_packed) {  // silu(gate) * up on the accumulators' way out
-          GemmArgs g1{k.moe_a16, W, (const bf16*)w.w_gu, W, k.moe_h16, F, nullptr, 0, nullptr, rows, 2 * F, W, EPI_SWIGLU, 0};
-          g1.m_tile_group = k.moe_tiles; g1.groups = E;
+          GemmArgs g1{k.moe_a16, W, (const bf16*)w.w_gu, W, k.moe_h16, F, nullptr, 0, nullptr, rows, 2 * F, W,
+                      eact == GLU_CLAMPED ? EPI_CLAMPGLU : EPI_SWIGLU, 0};
+          g1.m_tile_group = k.moe_tiles; g1.groups = E; g1.glu_limit = l.ff_limit;
           SPAN(0, 4.0 * rows * F * W, gemm_bf16_tn(stream_, g1));
         } else {
           GemmArgs g1{k.moe_a16, W, (const bf16*)w.w_gu, W, k.gu16, 2 * F, nullptr, 0, nullptr, rows, 2 * F, W, EPI_NONE, 0};

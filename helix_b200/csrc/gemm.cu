@@ -98,7 +98,7 @@ __global__ void __launch_bounds__(kNumThreads, 1)
 gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                const __grid_constant__ CUtensorMap map_c, const __grid_constant__ CUtensorMap map_r,
                const bf16* __restrict__ bias, int M, int N, int K, int tile_grp, int tile_group_n,
-               const __grid_constant__ RopeEpi rope, const int32_t* __restrict__ m_tile_group) {
+               const __grid_constant__ RopeEpi rope, const int32_t* __restrict__ m_tile_group, float glu_limit) {
   using C = Cfg<BN, CG>;
   constexpr int TILE_M = BLOCK_M * CG;  // rows of one UMMA tile (per CTA: BLOCK_M)
   const uint32_t cta_rank = (CG == 2) ? cluster_ctarank() : 0u;
@@ -107,7 +107,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   const int tile_workers = (CG == 2) ? (gridDim.x >> 1) : gridDim.x;
   constexpr int STAGES = C::STAGES;
   constexpr bool kF32 = (EPI == EPI_F32);
-  constexpr bool kSwiGLU = (EPI == EPI_SWIGLU || EPI == EPI_GEGLU);  // gated unit over [128 gate | 128 up] tiles
+  constexpr bool kSwiGLU = (EPI == EPI_SWIGLU || EPI == EPI_GEGLU || EPI == EPI_CLAMPGLU);  // gated unit over [128 gate | 128 up] tiles
   constexpr bool kResid = (EPI == EPI_RESID || EPI == EPI_BIAS_RESID);
   constexpr bool kBias = (EPI == EPI_BIAS || EPI == EPI_BIAS_GELU || EPI == EPI_BIAS_RESID);
   constexpr bool kRope = (EPI == EPI_ROPE);
@@ -390,8 +390,15 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
               tmem_ld_32x32b_x32(t_tile + 128 + col, u);
               tmem_ld_wait();
 #pragma unroll
-              for (int j = 0; j < 32; ++j)
-                f[j] = (EPI == EPI_GEGLU ? gelu_tanh_f(__uint_as_float(v[j])) : silu(__uint_as_float(v[j]))) * __uint_as_float(u[j]);
+              for (int j = 0; j < 32; ++j) {
+                if constexpr (EPI == EPI_CLAMPGLU) {
+                  const float gg = fminf(__uint_as_float(v[j]), glu_limit);
+                  const float uu = fminf(fmaxf(__uint_as_float(u[j]), -glu_limit), glu_limit);
+                  f[j] = gg / (1.0f + __expf(-1.702f * gg)) * (uu + 1.f);
+                } else {
+                  f[j] = (EPI == EPI_GEGLU ? gelu_tanh_f(__uint_as_float(v[j])) : silu(__uint_as_float(v[j]))) * __uint_as_float(u[j]);
+                }
+              }
             } else {
               tmem_ld_wait();
 #pragma unroll
@@ -474,7 +481,7 @@ template <int BN, int EPI, int CG>
 cudaError_t launch_cfg(cudaStream_t stream, const GemmArgs& g, int num_sms) {
   using C = Cfg<BN, CG>;
   constexpr bool kF32 = (EPI == EPI_F32);
-  constexpr bool kSwiGLU = (EPI == EPI_SWIGLU || EPI == EPI_GEGLU);
+  constexpr bool kSwiGLU = (EPI == EPI_SWIGLU || EPI == EPI_GEGLU || EPI == EPI_CLAMPGLU);
   constexpr int TILE_M = BLOCK_M * CG;
   CUtensorMap ma, mb, mc, mr;
   const int n_out = kSwiGLU ? g.N / 2 : g.N;
@@ -526,7 +533,7 @@ cudaError_t launch_cfg(cudaStream_t stream, const GemmArgs& g, int num_sms) {
   cfg.attrs = attr;
   cfg.numAttrs = (CG > 1) ? 1 : 0;
   static const int l2_hints = [] { const char* e = getenv("HB_GEMM_L2HINTS"); return e ? atoi(e) : 0; }();  // A/B knob
-  return cudaLaunchKernelEx(&cfg, kern, ma, mb, mc, mr, g.bias, g.M, g.N, g.K, grp, group_n | (l2_hints ? 2 : 0), g.rope, g.m_tile_group);
+  return cudaLaunchKernelEx(&cfg, kern, ma, mb, mc, mr, g.bias, g.M, g.N, g.K, grp, group_n | (l2_hints ? 2 : 0), g.rope, g.m_tile_group, g.glu_limit);
 }
 
 bool use_pair() {  // HB_GEMM_2CTA=0 falls back to single-CTA tiles (A/B measurements)
@@ -549,10 +556,10 @@ cudaError_t launch_epi(cudaStream_t stream, const GemmArgs& g, int num_sms) {
       if (use_pair() && !g.m_tile_group && (long)((g.M + 255) / 256) * ((g.N + 255) / 256) >= num_sms / 2) return launch_cfg<256, EPI, 2>(stream, g, num_sms);
       return launch_cfg<256, EPI, 1>(stream, g, num_sms);
     case 128:
-      if constexpr (EPI != EPI_SWIGLU && EPI != EPI_GEGLU && EPI != EPI_ROPE) return launch_cfg<128, EPI, 1>(stream, g, num_sms);
+      if constexpr (EPI != EPI_SWIGLU && EPI != EPI_GEGLU && EPI != EPI_CLAMPGLU && EPI != EPI_ROPE) return launch_cfg<128, EPI, 1>(stream, g, num_sms);
       return cudaErrorInvalidValue;
     case 64:
-      if constexpr (EPI != EPI_SWIGLU && EPI != EPI_GEGLU && EPI != EPI_ROPE) return launch_cfg<64, EPI, 1>(stream, g, num_sms);
+      if constexpr (EPI != EPI_SWIGLU && EPI != EPI_GEGLU && EPI != EPI_CLAMPGLU && EPI != EPI_ROPE) return launch_cfg<64, EPI, 1>(stream, g, num_sms);
       return cudaErrorInvalidValue;
     default: return cudaErrorInvalidValue;
   }
@@ -570,7 +577,7 @@ cudaError_t set_attr_epi() {
   cudaError_t e;
   if ((e = set_attr<256, EPI, 2>()) != cudaSuccess) return e;
   if ((e = set_attr<256, EPI, 1>()) != cudaSuccess) return e;
-  if constexpr (EPI != EPI_SWIGLU && EPI != EPI_GEGLU && EPI != EPI_ROPE) {
+  if constexpr (EPI != EPI_SWIGLU && EPI != EPI_GEGLU && EPI != EPI_CLAMPGLU && EPI != EPI_ROPE) {
     if ((e = set_attr<128, EPI, 1>()) != cudaSuccess) return e;
     return set_attr<64, EPI, 1>();
   }
@@ -588,6 +595,7 @@ cudaError_t gemm_init() {
   if ((e = set_attr_epi<EPI_F32>()) != cudaSuccess) return e;
   if ((e = set_attr_epi<EPI_ROPE>()) != cudaSuccess) return e;
   if ((e = set_attr_epi<EPI_GEGLU>()) != cudaSuccess) return e;
+  if ((e = set_attr_epi<EPI_CLAMPGLU>()) != cudaSuccess) return e;
   return set_attr_epi<EPI_SWIGLU>();
 }
 
@@ -626,6 +634,12 @@ cudaError_t gemm_bf16_tn(cudaStream_t stream, const GemmArgs& g) {
       GemmArgs h = g;
       h.block_n = 256;
       return launch_epi<EPI_GEGLU>(stream, h, sms);
+    }
+    case EPI_CLAMPGLU: {
+      if (g.N % 256) return cudaErrorInvalidValue;
+      GemmArgs h = g;
+      h.block_n = 256;
+      return launch_epi<EPI_CLAMPGLU>(stream, h, sms);
     }
     case EPI_F32: return launch_epi<EPI_F32>(stream, g, sms);
     case EPI_ROPE: {

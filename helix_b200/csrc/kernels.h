@@ -27,6 +27,8 @@ enum Epi : int {
                        // C[m, tile*128+j] = silu(gate_j) * up_j   (bf16, ldc counts N/2 columns)
   EPI_F32 = 6,         // C = acc                              (fp32)
   EPI_GEGLU = 8,       // as EPI_SWIGLU with gelu_tanh(gate_j) * up_j
+  EPI_CLAMPGLU = 9,    // as EPI_SWIGLU with g = min(gate_j, limit), u = clamp(up_j, -limit, limit): g sigmoid(1.702 g) (u + 1)
+                       // (limit = GemmArgs::glu_limit)
   EPI_ROPE = 7,        // fused QKV projection of a decoder: C = bf16(acc [+ bias]) with the q and k heads rotated
                        // (RopeEpi) and the k / v rows also scattered into the paged KV cache
 };
@@ -60,6 +62,7 @@ struct GemmArgs {
   // tile i of A multiply the matrix m_tile_group[i] (device array, ceil(M / 128) entries, every entry a valid group).
   const int32_t* m_tile_group = nullptr;
   int groups = 1;
+  float glu_limit = 0.f;  // EPI_CLAMPGLU
 };
 cudaError_t gemm_bf16_tn(cudaStream_t stream, const GemmArgs& a);
 // Debug/test-only CUDA-core GEMM (same contract, EPI_NONE/EPI_F32 only); used by tests as an on-device checker.

@@ -480,12 +480,13 @@ static size_t carve_stack(Model* m, const hb_stack_desc& d, const hb_layer_desc*
         const size_t Fs = l.shared_ff;
         uint8_t* sg = take(2 * Fs * W);
         uint8_t* sd = take(W * Fs);
-        put(p + "mlp.shared.gate", sg, 0, Fs, W);
-        put(p + "mlp.shared.up", sg, Fs, Fs, W);
+        const bool spk = !d.compute_f32 && Fs % 128 == 0;
+        put(p + "mlp.shared.gate", sg, 0, Fs, W, false, 1.f, false, spk ? 1 : 0);
+        put(p + "mlp.shared.up", sg, spk ? 0 : Fs, Fs, W, false, 1.f, false, spk ? 2 : 0);
         put(p + "mlp.shared.down", sd, 0, W, Fs);
-        w.w_gu_sh = sg; w.w_down_sh = sd;
+        w.w_gu_sh = sg; w.w_down_sh = sd; w.sh_packed = spk;
       }
-      const bool packed = !d.compute_f32 && Fn % 128 == 0 && l.expert_kind == HB_EXPERT_SILU;
+      const bool packed = !d.compute_f32 && Fn % 128 == 0;
       for (size_t e = 0; e < E; ++e) {
         const std::string pe = p + "mlp.e" + std::to_string(e) + ".";
         put(pe + "gate", gu, e * 2 * Fn, Fn, W, false, 1.f, false, packed ? 1 : 0);

@@ -55,6 +55,7 @@ struct StackLayerW {
   // bf16 mode, ff a multiple of 128 (tanh-GELU unit, experts): [gate | up] rows stored per 256-row tile as [128 gate | 128 up],
   // the layout the gated epilogue of the tcgen05 GEMM reads; every other consumer indexes through it
   bool gu_packed = false;
+  bool sh_packed = false;  // the same for the unit every token of a mixture uses
 };
 
 // where an uploaded checkpoint tensor lands inside the arena

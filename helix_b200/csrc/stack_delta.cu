@@ -11,6 +11,7 @@
 
 #include "kernels.h"
 #include "launch.h"
+#include "ptx.cuh"
 #include "stack_common.cuh"
 
 namespace hb {
@@ -101,61 +102,77 @@ __device__ __forceinline__ void cp_async4(float* smem_dst, const float* gsrc) {
   const unsigned d = (unsigned)__cvta_generic_to_shared(smem_dst);
   asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(d), "l"(gsrc) : "memory");
 }
+__device__ __forceinline__ void cp_async16(float* smem_dst, const float* gsrc) {
+  const unsigned d = (unsigned)__cvta_generic_to_shared(smem_dst);
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(d), "l"(gsrc) : "memory");
+}
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
-// Block = (entry, head, 32 value columns), 256 threads: a state column is shared by 8 lanes, lane `sub` of them keeps the key
-// channels 4 (sub + 8 i) .. + 3, i < CPL / 4, in registers (the 8 lanes of a column read 128 contiguous bytes of q or k per
-// step).  Per token both products with the OLD state, S^T k and S^T q, are formed in one pass and added over the 8 lanes by a
-// butterfly; the write u and the output o = g S^T q + (k . q) u follow from them, then the state is updated in place.
-// Tokens are staged kDelTch at a time through a cp.async double buffer.
+// Block = (entry, head, 32 value columns), 128 threads: a group of 8 lanes owns TWO state columns (c and c + 16 of the slice),
+// lane `sub` of the group keeps the key channels 4 (sub + 8 i) .. + 3, i < CPL / 4, of both in registers as packed pairs of
+// neighbouring channels, so one 16-byte read of q or k from shared memory feeds four f32x2 products and the 8 lanes of a
+// group read 128 contiguous bytes.  Per token both products with the OLD state, S^T k and S^T q, are formed in one pass and
+// added over the 8 lanes by a butterfly; the write u and the output o = g S^T q + (k . q) u follow from them, then the state
+// is updated in place (g S + k u: one multiply and one fused multiply-add per pair).  Tokens are staged kDelTch at a time
+// through a cp.async double buffer.
+constexpr int kDelThreads = 128;
 template <int CPL>
-__global__ void __launch_bounds__(256) delta_recurrence_kernel(DeltaArgs a) {
+__global__ void __launch_bounds__(kDelThreads) delta_recurrence_kernel(DeltaArgs a) {
   constexpr int DP = 8 * CPL;                     // padded key channels
   constexpr int per_tok = 2 * DP + 32 + 4;        // q | k | v (this block's columns) | beta, decay, k.q, pad
   constexpr int stage_floats = kDelTch * per_tok;
-  extern __shared__ float sm[];                   // 2 stages + outputs [kDelTch][32]
+  extern __shared__ __align__(16) float sm[];     // 2 stages + outputs [kDelTch][32]
   float* obuf = sm + 2 * stage_floats;
   const int b = blockIdx.x, h = blockIdx.y, kvh = h / (a.H / a.G);
   const int lane = threadIdx.x & 31, w = threadIdx.x >> 5, sub = lane & 7;
-  const int col = w * 4 + (lane >> 3);            // column of this block's slice
-  const int j = blockIdx.z * 32 + col;
-  const bool live = j < a.Dv;
+  const int col = w * 4 + (lane >> 3);            // first column of this group inside the slice; the second is col + 16
+  const int j0 = blockIdx.z * 32 + col, j1 = j0 + 16;
+  const bool live0 = j0 < a.Dv, live1 = j1 < a.Dv;
   const int t0 = a.cu[b], t1 = a.cu[b + 1];
   const int D = a.D;
   float* st = a.state + (size_t)a.slots[b] * a.slot_stride + (size_t)h * D * a.Dv;
   const bool fresh = a.first_pos[b] == 0;
-  float S[CPL];
+  uint64_t Sa[CPL / 2], Sb[CPL / 2];
 #pragma unroll
   for (int i = 0; i < CPL / 4; ++i)
 #pragma unroll
-    for (int e = 0; e < 4; ++e) {
-      const int ch = 4 * (sub + 8 * i) + e;
-      S[4 * i + e] = (!fresh && live && ch < D) ? st[(size_t)ch * a.Dv + j] : 0.f;
+    for (int e = 0; e < 2; ++e) {
+      const int ch = 4 * (sub + 8 * i) + 2 * e;
+      auto ld = [&](int c, int j, bool live) { return (!fresh && live && c < D) ? st[(size_t)c * a.Dv + j] : 0.f; };
+      Sa[2 * i + e] = f2_pack(ld(ch, j0, live0), ld(ch + 1, j0, live0));
+      Sb[2 * i + e] = f2_pack(ld(ch, j1, live1), ld(ch + 1, j1, live1));
     }
   for (int e = threadIdx.x; e < 2 * stage_floats; e += blockDim.x) sm[e] = 0.f;  // padded channels read zeros
   __syncthreads();
-  auto issue = [&](int tc, int stage) {
+  // 16-byte copies when every row piece starts on a 16-byte boundary
+  const bool vec = ((D | a.Dv | (int)a.ld | a.off_q | a.off_k | a.off_v) & 3) == 0 && ((uintptr_t)a.in & 15) == 0;
+  const int nw = blockDim.x >> 5;
+  auto issue = [&](int tc, int stage) {  // warp w stages the tokens w, w + nw, ...: no index arithmetic beyond adds
     const int nt = min(kDelTch, t1 - tc);
     float* base = sm + stage * stage_floats;
-    for (int e = threadIdx.x; e < nt * D; e += blockDim.x) {
-      const int tt = e / D, i = e % D;
+    for (int tt = w; tt < nt; tt += nw) {
       const float* src = a.in + (size_t)(tc + tt) * a.ld;
+      const float* sq = src + a.off_q + kvh * D;
+      const float* sk = src + a.off_k + kvh * D;
+      const float* sv = src + a.off_v + (size_t)h * a.Dv + blockIdx.z * 32;
       float* dst = base + tt * per_tok;
-      cp_async4(dst + i, src + a.off_q + kvh * D + i);
-      cp_async4(dst + DP + i, src + a.off_k + kvh * D + i);
-    }
-    for (int e = threadIdx.x; e < nt * 32; e += blockDim.x) {
-      const int tt = e >> 5, c = e & 31;
-      if (blockIdx.z * 32 + c < a.Dv)
-        cp_async4(base + tt * per_tok + 2 * DP + c, a.in + (size_t)(tc + tt) * a.ld + a.off_v + (size_t)h * a.Dv + blockIdx.z * 32 + c);
-    }
-    for (int tt = threadIdx.x; tt < nt; tt += blockDim.x) {
-      const float* src = a.in + (size_t)(tc + tt) * a.ld;
-      float* dst = base + tt * per_tok + 2 * DP + 32;
-      cp_async4(dst, src + a.off_beta + h);
-      cp_async4(dst + 1, src + a.off_decay + h);
-      cp_async4(dst + 2, src + a.off_kq + kvh);
+      if (vec) {
+        for (int i = lane * 4; i < D; i += 128) {
+          cp_async16(dst + i, sq + i);
+          cp_async16(dst + DP + i, sk + i);
+        }
+        if (lane < 8 && blockIdx.z * 32 + lane * 4 < a.Dv) cp_async16(dst + 2 * DP + lane * 4, sv + lane * 4);
+      } else {
+        for (int i = lane; i < D; i += 32) {
+          cp_async4(dst + i, sq + i);
+          cp_async4(dst + DP + i, sk + i);
+        }
+        if (blockIdx.z * 32 + lane < a.Dv) cp_async4(dst + 2 * DP + lane, sv + lane);
+      }
+      if (lane == 8) cp_async4(dst + 2 * DP + 32, src + a.off_beta + h);
+      if (lane == 9) cp_async4(dst + 2 * DP + 33, src + a.off_decay + h);
+      if (lane == 10) cp_async4(dst + 2 * DP + 34, src + a.off_kq + kvh);
     }
     cp_async_commit();
   };
@@ -173,36 +190,45 @@ __global__ void __launch_bounds__(256) delta_recurrence_kernel(DeltaArgs a) {
     const float* base = sm + stage * stage_floats;
     for (int tt = 0; tt < nt; ++tt) {
       const float* tk = base + tt * per_tok;
-      const float4* q4 = reinterpret_cast<const float4*>(tk);
-      const float4* k4 = reinterpret_cast<const float4*>(tk + DP);
-      const float vj = tk[2 * DP + col];
+      const ulonglong2* q2 = reinterpret_cast<const ulonglong2*>(tk);
+      const ulonglong2* k2 = reinterpret_cast<const ulonglong2*>(tk + DP);
+      const float va = tk[2 * DP + col], vb = tk[2 * DP + col + 16];
       const float beta = tk[2 * DP + 32], g = tk[2 * DP + 33], kq = tk[2 * DP + 34];
-      float4 kk[CPL / 4];
-      float sk0 = 0.f, sk1 = 0.f, sq0 = 0.f, sq1 = 0.f;
+      uint64_t kk[CPL / 2];
+      uint64_t ka = 0, qa = 0, kb = 0, qb = 0;  // packed (0, 0): S^T k and S^T q of the two columns
 #pragma unroll
       for (int i = 0; i < CPL / 4; ++i) {
-        const float4 q = q4[sub + 8 * i];
-        kk[i] = k4[sub + 8 * i];
-        sk0 = fmaf(S[4 * i + 0], kk[i].x, sk0); sk1 = fmaf(S[4 * i + 1], kk[i].y, sk1);
-        sk0 = fmaf(S[4 * i + 2], kk[i].z, sk0); sk1 = fmaf(S[4 * i + 3], kk[i].w, sk1);
-        sq0 = fmaf(S[4 * i + 0], q.x, sq0); sq1 = fmaf(S[4 * i + 1], q.y, sq1);
-        sq0 = fmaf(S[4 * i + 2], q.z, sq0); sq1 = fmaf(S[4 * i + 3], q.w, sq1);
+        const ulonglong2 q = q2[sub + 8 * i], kv = k2[sub + 8 * i];
+        kk[2 * i] = kv.x;
+        kk[2 * i + 1] = kv.y;
+        ka = f2_fma(Sa[2 * i], kv.x, ka); ka = f2_fma(Sa[2 * i + 1], kv.y, ka);
+        qa = f2_fma(Sa[2 * i], q.x, qa);  qa = f2_fma(Sa[2 * i + 1], q.y, qa);
+        kb = f2_fma(Sb[2 * i], kv.x, kb); kb = f2_fma(Sb[2 * i + 1], kv.y, kb);
+        qb = f2_fma(Sb[2 * i], q.x, qb);  qb = f2_fma(Sb[2 * i + 1], q.y, qb);
       }
-      float sk = sk0 + sk1, sq = sq0 + sq1;
+      float x0, x1, ska, sqa, skb, sqb;
+      f2_unpack(ka, x0, x1); ska = x0 + x1;
+      f2_unpack(qa, x0, x1); sqa = x0 + x1;
+      f2_unpack(kb, x0, x1); skb = x0 + x1;
+      f2_unpack(qb, x0, x1); sqb = x0 + x1;
 #pragma unroll
       for (int o = 1; o < 8; o <<= 1) {
-        sk += __shfl_xor_sync(0xffffffffu, sk, o);
-        sq += __shfl_xor_sync(0xffffffffu, sq, o);
+        ska += __shfl_xor_sync(0xffffffffu, ska, o);
+        sqa += __shfl_xor_sync(0xffffffffu, sqa, o);
+        skb += __shfl_xor_sync(0xffffffffu, skb, o);
+        sqb += __shfl_xor_sync(0xffffffffu, sqb, o);
       }
-      const float u = beta * (vj - g * sk);
+      const float ua = beta * (va - g * ska), ub = beta * (vb - g * skb);
+      const uint64_t ua2 = f2_pack(ua, ua), ub2 = f2_pack(ub, ub), g2 = f2_pack(g, g);
 #pragma unroll
-      for (int i = 0; i < CPL / 4; ++i) {
-        S[4 * i + 0] = fmaf(kk[i].x, u, g * S[4 * i + 0]);
-        S[4 * i + 1] = fmaf(kk[i].y, u, g * S[4 * i + 1]);
-        S[4 * i + 2] = fmaf(kk[i].z, u, g * S[4 * i + 2]);
-        S[4 * i + 3] = fmaf(kk[i].w, u, g * S[4 * i + 3]);
+      for (int i = 0; i < CPL / 2; ++i) {
+        Sa[i] = f2_fma(kk[i], ua2, f2_mul(g2, Sa[i]));
+        Sb[i] = f2_fma(kk[i], ub2, f2_mul(g2, Sb[i]));
       }
-      if (sub == 0) obuf[tt * 32 + col] = fmaf(kq, u, g * sq);
+      if (sub == 0) {
+        obuf[tt * 32 + col] = fmaf(kq, ua, g * sqa);
+        obuf[tt * 32 + col + 16] = fmaf(kq, ub, g * sqb);
+      }
     }
     __syncthreads();
     for (int e = threadIdx.x; e < nt * 32; e += blockDim.x) {
@@ -211,15 +237,19 @@ __global__ void __launch_bounds__(256) delta_recurrence_kernel(DeltaArgs a) {
     }
     __syncthreads();  // the stage and the outputs are rewritten in the next iteration
   }
-  if (live) {
 #pragma unroll
-    for (int i = 0; i < CPL / 4; ++i)
+  for (int i = 0; i < CPL / 4; ++i)
 #pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        const int ch = 4 * (sub + 8 * i) + e;
-        if (ch < D) st[(size_t)ch * a.Dv + j] = S[4 * i + e];
-      }
-  }
+    for (int e = 0; e < 2; ++e) {
+      const int ch = 4 * (sub + 8 * i) + 2 * e;
+      float s0, s1;
+      f2_unpack(Sa[2 * i + e], s0, s1);
+      if (live0 && ch < D) st[(size_t)ch * a.Dv + j0] = s0;
+      if (live0 && ch + 1 < D) st[(size_t)(ch + 1) * a.Dv + j0] = s1;
+      f2_unpack(Sb[2 * i + e], s0, s1);
+      if (live1 && ch < D) st[(size_t)ch * a.Dv + j1] = s0;
+      if (live1 && ch + 1 < D) st[(size_t)(ch + 1) * a.Dv + j1] = s1;
+    }
 }
 
 template <int CPL>
@@ -227,7 +257,7 @@ cudaError_t launch_delta(cudaStream_t s, const DeltaArgs& a) {
   constexpr int DP = 8 * CPL;
   const size_t smem = (size_t)(2 * kDelTch * (2 * DP + 36) + kDelTch * 32) * 4;
   dim3 grid(a.B, a.H, (a.Dv + 31) / 32);
-  delta_recurrence_kernel<CPL><<<grid, 256, smem, s>>>(a);
+  delta_recurrence_kernel<CPL><<<grid, kDelThreads, smem, s>>>(a);
   return cudaGetLastError();
 }
 

@@ -462,6 +462,38 @@ def test_mixed_batches_match_each_request_alone(f32):
         assert not oks[i].any() or row_err(g, solo[i])[oks[i]].max() < (1e-5 if f32 else 3e-2)
 
 
+def test_mixed_steps_on_the_fused_attention_kernel():
+    # serving mode, head size of the tcgen05 kernels: steps that carry a long portion run every entry on the fused kernel, so
+    # single tokens and two-token portions of other sequences are short items of the same launch, each with its own window start
+    cfg = ref.random_config(width=128, vocab=256, heads=4, kv_heads=2, dim=64, vdim=64, window=90,
+                            order=(("attention", "dense"), ("delta", None), ("attention", None)))
+    sd = ref.random_state_dict(cfg, seed=33)
+    o = ref.LatanexOracle(cfg, sd)
+    seqs = [tokens(30 + i, n, cfg["vocab"]) for i, n in enumerate((300, 140, 170))]
+    want = [o.forward(s) for s in seqs]
+    plans = [[100, 100, 64, 36], [1] * 3 + [70, 2, 65], [2, 2, 99, 1, 66]]
+    with make_engine(cfg, sd, 0) as e:
+        ids = [e.seq_open() for _ in seqs]
+        at, got = [0] * 3, [[] for _ in seqs]
+        while any(at[i] < len(seqs[i]) for i in range(3)):
+            entries, who = [], []
+            for i in range(3):
+                if at[i] >= len(seqs[i]):
+                    continue
+                n = min(plans[i].pop(0) if plans[i] else 1, len(seqs[i]) - at[i])
+                entries.append((ids[i], seqs[i][at[i]:at[i] + n], list(range(n))))
+                who.append((i, n))
+                at[i] += n
+            out, r = e.seq_step(entries), 0
+            for i, n in who:
+                got[i].append(out[r:r + n])
+                r += n
+        for sid in ids:
+            e.seq_close(sid)
+    for i in range(3):
+        assert row_err(np.concatenate(got[i]), want[i]).max() < TOL[0]
+
+
 def test_pages_and_slots_are_reused():
     cfg = ref.random_config()
     sd = slow_decay(ref.random_state_dict(cfg, seed=37), layer=1)  # a state left behind by the slot's last owner would show

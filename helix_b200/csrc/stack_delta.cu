@@ -22,13 +22,32 @@ __device__ __forceinline__ float softplusf_(float z) { return fmaxf(z, 0.f) + lo
 // One block per token.  dynamic smem: the token's convolved, activated q | k | v row [C]
 template <typename WT>
 __global__ void __launch_bounds__(256) delta_prep_kernel(DeltaPrepArgs a) {
-  extern __shared__ float row[];
+  extern __shared__ __align__(16) float row[];
   const int t = blockIdx.x;
   const int b = a.seq_of[t], t0 = a.cu[b];
   const int GD = a.G * a.D, C = 2 * GD + a.H * a.Dv, taps = a.taps;
   const bool fresh = a.first_pos[b] == 0;
   const float* tail = a.state + (size_t)a.slots[b] * a.slot_stride + a.tail_off;  // [taps - 1][C]: inputs of positions first - (taps - 1) ..
   const WT* cw = (const WT*)a.conv_w;
+  if (((C | (int)a.ldp | a.off_qkv) & 3) == 0 && ((uintptr_t)a.p & 15) == 0 && ((uintptr_t)a.state & 15) == 0 &&
+      ((a.slot_stride | (long)a.tail_off) & 3) == 0) {
+    // four neighbouring channels per thread: 16-byte loads of the projection rows and of the slot's tail
+    for (int c = threadIdx.x * 4; c < C; c += blockDim.x * 4) {
+      float acc[4] = {0.f, 0.f, 0.f, 0.f};
+      for (int j = 0; j < taps; ++j) {
+        const int tau = t - (taps - 1 - j);
+        float4 x = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (tau >= t0) x = *reinterpret_cast<const float4*>(a.p + (size_t)tau * a.ldp + a.off_qkv + c);
+        else if (!fresh) x = *reinterpret_cast<const float4*>(tail + (size_t)(tau - t0 + taps - 1) * C + c);
+        acc[0] = fmaf(ldf<WT>(cw, (size_t)c * taps + j), x.x, acc[0]);
+        acc[1] = fmaf(ldf<WT>(cw, (size_t)(c + 1) * taps + j), x.y, acc[1]);
+        acc[2] = fmaf(ldf<WT>(cw, (size_t)(c + 2) * taps + j), x.z, acc[2]);
+        acc[3] = fmaf(ldf<WT>(cw, (size_t)(c + 3) * taps + j), x.w, acc[3]);
+      }
+#pragma unroll
+      for (int e = 0; e < 4; ++e) row[c + e] = acc[e] * sigmoidf_(acc[e]);
+    }
+  } else {
   for (int c = threadIdx.x; c < C; c += blockDim.x) {
     float acc = 0.f;
     for (int j = 0; j < taps; ++j) {  // tap j multiplies the input of token t - (taps - 1 - j), oldest first
@@ -39,6 +58,7 @@ __global__ void __launch_bounds__(256) delta_prep_kernel(DeltaPrepArgs a) {
       acc = fmaf(ldf<WT>(cw, (size_t)c * taps + j), x, acc);
     }
     row[c] = acc * sigmoidf_(acc);
+  }
   }
   __syncthreads();
   const int w = threadIdx.x >> 5, l = threadIdx.x & 31, nw = blockDim.x >> 5;
@@ -64,7 +84,12 @@ __global__ void __launch_bounds__(256) delta_prep_kernel(DeltaPrepArgs a) {
     qk = warp_sum(qk);
     if (l == 0) out[C + 2 * a.H + g] = qk;
   }
-  for (int i = threadIdx.x; i < a.H * a.Dv; i += blockDim.x) out[2 * GD + i] = row[2 * GD + i];
+  if (((GD | (a.H * a.Dv) | (int)a.ldo) & 3) == 0 && ((uintptr_t)a.out & 15) == 0) {
+    for (int i = threadIdx.x * 4; i < a.H * a.Dv; i += blockDim.x * 4)
+      *reinterpret_cast<float4*>(out + 2 * GD + i) = *reinterpret_cast<const float4*>(row + 2 * GD + i);
+  } else {
+    for (int i = threadIdx.x; i < a.H * a.Dv; i += blockDim.x) out[2 * GD + i] = row[2 * GD + i];
+  }
   const WT* adt = (const WT*)a.a_dt;
   for (int h = threadIdx.x; h < a.H; h += blockDim.x) {
     const float* pr = a.p + (size_t)t * a.ldp;

@@ -185,16 +185,29 @@ __global__ void __launch_bounds__(256) gqa_prep_vec_kernel(GqaPrepArgs a) {
 // dynamic smem: the token's q | k rows [(H + G) * D] + per-head factors [H + G]
 template <typename CT>
 __global__ void __launch_bounds__(256) gqa_prep_token_kernel(GqaPrepArgs a) {
-  extern __shared__ float sm[];
+  extern __shared__ __align__(16) float sm[];
   __shared__ float red[32];
   const int t = blockIdx.x;
   const int nq = a.H * a.D, nk = a.G * a.D, nv = a.G * a.Dv;
   float* rsh = sm + nq + nk;
   const float* pr = a.p + (size_t)t * a.ldp;
   const CT* bias = (const CT*)a.bias;
-  for (int i = threadIdx.x; i < nq + nk; i += blockDim.x) {
-    const int col = i < nq ? a.q_off + i : a.k_off + (i - nq);
-    sm[i] = pr[col] + (bias ? ldf<CT>(bias, col) : 0.f);
+  // 16-byte pieces when q, k and v rows start on 16-byte boundaries and the sizes are multiples of four
+  const bool vec = ((nq | nk | nv | a.D | a.Dv | (int)a.ldp | a.q_off | a.k_off | a.v_off | (int)a.ldq) & 3) == 0 && ((uintptr_t)a.p & 15) == 0 &&
+                   ((uintptr_t)a.q & 15) == 0 && ((uintptr_t)a.q_b16 & 7) == 0 && ((uintptr_t)a.v_first & 15) == 0 &&
+                   ((uintptr_t)a.k_cache & 15) == 0 && ((uintptr_t)a.v_cache & 15) == 0;
+  if (vec) {
+    for (int i = threadIdx.x * 4; i < nq + nk; i += blockDim.x * 4) {
+      const int col = i < nq ? a.q_off + i : a.k_off + (i - nq);
+      float4 v = *reinterpret_cast<const float4*>(pr + col);
+      if (bias) { v.x += ldf<CT>(bias, col); v.y += ldf<CT>(bias, col + 1); v.z += ldf<CT>(bias, col + 2); v.w += ldf<CT>(bias, col + 3); }
+      *reinterpret_cast<float4*>(sm + i) = v;
+    }
+  } else {
+    for (int i = threadIdx.x; i < nq + nk; i += blockDim.x) {
+      const int col = i < nq ? a.q_off + i : a.k_off + (i - nq);
+      sm[i] = pr[col] + (bias ? ldf<CT>(bias, col) : 0.f);
+    }
   }
   __syncthreads();
   const int half = a.rope_dims / 2;
@@ -230,13 +243,65 @@ __global__ void __launch_bounds__(256) gqa_prep_token_kernel(GqaPrepArgs a) {
     __syncthreads();
   }
   const CT* gain = (const CT*)a.qk_gain;
+  const int slot = a.slots ? a.slots[t] : -1;
+  const size_t page = slot >= 0 ? slot / a.page_size : 0, off = slot >= 0 ? slot % a.page_size : 0;
+  const float lam = a.blend_role == 2 ? ldf<CT>((const CT*)a.vmix, 0) : 0.f;
+  auto put4 = [](CT* dst, const float4& x) {  // four neighbouring cache / weight-typed elements
+    if (sizeof(CT) == 4) {
+      *reinterpret_cast<float4*>(dst) = x;
+    } else {
+      __nv_bfloat162 lo = __floats2bfloat162_rn(x.x, x.y), hi = __floats2bfloat162_rn(x.z, x.w);
+      uint2 pk;
+      pk.x = *reinterpret_cast<unsigned*>(&lo);
+      pk.y = *reinterpret_cast<unsigned*>(&hi);
+      *reinterpret_cast<uint2*>(dst) = pk;
+    }
+  };
+  if (vec) {
+    for (int i = threadIdx.x * 4; i < nq + nk; i += blockDim.x * 4) {
+      const bool isq = i < nq;
+      const int head = isq ? i / a.D : a.H + (i - nq) / a.D;
+      float4 v = *reinterpret_cast<const float4*>(sm + i);
+      if (a.proj_norm) {
+        const float r = isq ? rq : rk;
+        v.x *= r * ldf<CT>(gain, i); v.y *= r * ldf<CT>(gain, i + 1); v.z *= r * ldf<CT>(gain, i + 2); v.w *= r * ldf<CT>(gain, i + 3);
+      } else if (a.unit_norm) {
+        const float r = rsh[head];
+        v.x *= r; v.y *= r; v.z *= r; v.w *= r;
+      }
+      if (isq) {
+        if (a.q) *reinterpret_cast<float4*>(a.q + (size_t)t * a.ldq + i) = v;
+        if (a.q_b16) {
+          __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y), hi = __floats2bfloat162_rn(v.z, v.w);
+          uint2 pk;
+          pk.x = *reinterpret_cast<unsigned*>(&lo);
+          pk.y = *reinterpret_cast<unsigned*>(&hi);
+          *reinterpret_cast<uint2*>(a.q_b16 + (size_t)t * a.ldq + i) = pk;
+        }
+      } else if (slot >= 0) {
+        const int kh = head - a.H, e = (i - nq) % a.D;
+        put4((CT*)a.k_cache + ((page * a.G + kh) * a.page_size + off) * a.D + e, v);
+      }
+    }
+    for (int i = threadIdx.x * 4; i < nv; i += blockDim.x * 4) {
+      float4 v = *reinterpret_cast<const float4*>(pr + a.v_off + i);
+      if (bias) { v.x += ldf<CT>(bias, a.v_off + i); v.y += ldf<CT>(bias, a.v_off + i + 1); v.z += ldf<CT>(bias, a.v_off + i + 2); v.w += ldf<CT>(bias, a.v_off + i + 3); }
+      if (a.blend_role == 1) {
+        *reinterpret_cast<float4*>(a.v_first + (size_t)t * nv + i) = v;
+      } else if (a.blend_role == 2) {
+        const float4 f = *reinterpret_cast<const float4*>(a.v_first + (size_t)t * nv + i);
+        v.x = (1.f - lam) * v.x + lam * f.x; v.y = (1.f - lam) * v.y + lam * f.y;
+        v.z = (1.f - lam) * v.z + lam * f.z; v.w = (1.f - lam) * v.w + lam * f.w;
+      }
+      if (slot >= 0) put4((CT*)a.v_cache + ((page * a.G + i / a.Dv) * a.page_size + off) * a.Dv + i % a.Dv, v);
+    }
+    return;
+  }
   for (int i = threadIdx.x; i < nq; i += blockDim.x) {
     const float v = sm[i] * (a.proj_norm ? rq * ldf<CT>(gain, i) : (a.unit_norm ? rsh[i / a.D] : 1.f));
     if (a.q) a.q[(size_t)t * a.ldq + i] = v;
     if (a.q_b16) a.q_b16[(size_t)t * a.ldq + i] = __float2bfloat16(v);
   }
-  const int slot = a.slots ? a.slots[t] : -1;
-  const size_t page = slot >= 0 ? slot / a.page_size : 0, off = slot >= 0 ? slot % a.page_size : 0;
   if (slot >= 0) {
     for (int i = threadIdx.x; i < nk; i += blockDim.x) {
       const int head = i / a.D;
@@ -244,7 +309,6 @@ __global__ void __launch_bounds__(256) gqa_prep_token_kernel(GqaPrepArgs a) {
       stf<CT>((CT*)a.k_cache, ((page * a.G + head) * a.page_size + off) * a.D + i % a.D, v);
     }
   }
-  const float lam = a.blend_role == 2 ? ldf<CT>((const CT*)a.vmix, 0) : 0.f;
   for (int i = threadIdx.x; i < nv; i += blockDim.x) {
     float v = pr[a.v_off + i] + (bias ? ldf<CT>(bias, a.v_off + i) : 0.f);
     if (a.blend_role == 1) a.v_first[(size_t)t * nv + i] = v;

@@ -12,10 +12,17 @@
 //     [page][kv_head][64][D] layout, so prompt portions and single-token steps run on that path's fused tcgen05 attention
 //     kernels (block mask, unit sink and head gate are parameters of both); other shapes, short portions and the exact
 //     mode take the per-token kernel;
-//   * the residual step norms the sum (x <- norm(alpha x + f(x))) or the sublayer's output (x <- x + norm(f(x)));
-//   * feed-forwards: clamped gated unit, tanh-GELU gated unit (gated epilogue of the GEMM), mixture of experts (router and
-//     choice in fp32, items sorted by expert into 128-row segments on the device, two grouped tcgen05 products; nothing
-//     returns to the host, so decode graphs stay static).
+//   * the residual step norms the sum (x <- norm(alpha x + f(x))), the sublayer's output (x <- x + norm(f(x))), or both sides
+//     (x <- x + norm_b(f(norm_a(x))): the sublayers then read the normed copy of the stream, and one launch adds a sublayer's
+//     normed output and norms the next sublayer's input); norms are RMS norms or element-wise tanh norms;
+//   * grouped-query layers may carry projection biases, a norm over the whole q / k projection, capped scores, learned sinks,
+//     sliding windows (all parameters of the fused attention kernels too) and values blended with an earlier layer's;
+//   * gated-delta-rule layers keep, per sequence slot, one fp32 matrix per head and the last inputs of their short
+//     convolutions; like the GLA state both start from zero inside the kernels when an entry starts at position 0;
+//   * feed-forwards: clamped, silu and tanh-GELU gated units (gated epilogues of the GEMM), mixture of experts (softmax or
+//     sigmoid router with an optional restriction to the best groups of experts, choice in fp32, items sorted by expert into
+//     128-row segments on the device, two grouped tcgen05 products, an optional unit every token uses; nothing returns to the
+//     host, so decode graphs stay static).
 #include "engine.h"
 #include "launch.h"
 

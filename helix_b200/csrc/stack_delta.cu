@@ -11,7 +11,6 @@
 
 #include "kernels.h"
 #include "launch.h"
-#include "ptx.cuh"
 #include "stack_common.cuh"
 
 namespace hb {
@@ -158,15 +157,15 @@ __global__ void __launch_bounds__(kDelThreads) delta_recurrence_kernel(DeltaArgs
   const int D = a.D;
   float* st = a.state + (size_t)a.slots[b] * a.slot_stride + (size_t)h * D * a.Dv;
   const bool fresh = a.first_pos[b] == 0;
-  uint64_t Sa[CPL / 2], Sb[CPL / 2];
+  float2 Sa[CPL / 2], Sb[CPL / 2];
 #pragma unroll
   for (int i = 0; i < CPL / 4; ++i)
 #pragma unroll
     for (int e = 0; e < 2; ++e) {
       const int ch = 4 * (sub + 8 * i) + 2 * e;
       auto ld = [&](int c, int j, bool live) { return (!fresh && live && c < D) ? st[(size_t)c * a.Dv + j] : 0.f; };
-      Sa[2 * i + e] = f2_pack(ld(ch, j0, live0), ld(ch + 1, j0, live0));
-      Sb[2 * i + e] = f2_pack(ld(ch, j1, live1), ld(ch + 1, j1, live1));
+      Sa[2 * i + e] = make_float2(ld(ch, j0, live0), ld(ch + 1, j0, live0));
+      Sb[2 * i + e] = make_float2(ld(ch, j1, live1), ld(ch + 1, j1, live1));
     }
   for (int e = threadIdx.x; e < 2 * stage_floats; e += blockDim.x) sm[e] = 0.f;  // padded channels read zeros
   __syncthreads();
@@ -215,27 +214,24 @@ __global__ void __launch_bounds__(kDelThreads) delta_recurrence_kernel(DeltaArgs
     const float* base = sm + stage * stage_floats;
     for (int tt = 0; tt < nt; ++tt) {
       const float* tk = base + tt * per_tok;
-      const ulonglong2* q2 = reinterpret_cast<const ulonglong2*>(tk);
-      const ulonglong2* k2 = reinterpret_cast<const ulonglong2*>(tk + DP);
+      const float4* q4 = reinterpret_cast<const float4*>(tk);
+      const float4* k4 = reinterpret_cast<const float4*>(tk + DP);
       const float va = tk[2 * DP + col], vb = tk[2 * DP + col + 16];
       const float beta = tk[2 * DP + 32], g = tk[2 * DP + 33], kq = tk[2 * DP + 34];
-      uint64_t kk[CPL / 2];
-      uint64_t ka = 0, qa = 0, kb = 0, qb = 0;  // packed (0, 0): S^T k and S^T q of the two columns
+      float2 kk[CPL / 2];
+      float2 ka = make_float2(0.f, 0.f), qa = ka, kb = ka, qb = ka;  // S^T k and S^T q of the two columns, even / odd channels
 #pragma unroll
       for (int i = 0; i < CPL / 4; ++i) {
-        const ulonglong2 q = q2[sub + 8 * i], kv = k2[sub + 8 * i];
-        kk[2 * i] = kv.x;
-        kk[2 * i + 1] = kv.y;
-        ka = f2_fma(Sa[2 * i], kv.x, ka); ka = f2_fma(Sa[2 * i + 1], kv.y, ka);
-        qa = f2_fma(Sa[2 * i], q.x, qa);  qa = f2_fma(Sa[2 * i + 1], q.y, qa);
-        kb = f2_fma(Sb[2 * i], kv.x, kb); kb = f2_fma(Sb[2 * i + 1], kv.y, kb);
-        qb = f2_fma(Sb[2 * i], q.x, qb);  qb = f2_fma(Sb[2 * i + 1], q.y, qb);
+        const float4 q = q4[sub + 8 * i], kv = k4[sub + 8 * i];
+        const float2 q0 = make_float2(q.x, q.y), q1 = make_float2(q.z, q.w);
+        kk[2 * i] = make_float2(kv.x, kv.y);
+        kk[2 * i + 1] = make_float2(kv.z, kv.w);
+        ka = __ffma2_rn(Sa[2 * i], kk[2 * i], ka); ka = __ffma2_rn(Sa[2 * i + 1], kk[2 * i + 1], ka);
+        qa = __ffma2_rn(Sa[2 * i], q0, qa);        qa = __ffma2_rn(Sa[2 * i + 1], q1, qa);
+        kb = __ffma2_rn(Sb[2 * i], kk[2 * i], kb); kb = __ffma2_rn(Sb[2 * i + 1], kk[2 * i + 1], kb);
+        qb = __ffma2_rn(Sb[2 * i], q0, qb);        qb = __ffma2_rn(Sb[2 * i + 1], q1, qb);
       }
-      float x0, x1, ska, sqa, skb, sqb;
-      f2_unpack(ka, x0, x1); ska = x0 + x1;
-      f2_unpack(qa, x0, x1); sqa = x0 + x1;
-      f2_unpack(kb, x0, x1); skb = x0 + x1;
-      f2_unpack(qb, x0, x1); sqb = x0 + x1;
+      float ska = ka.x + ka.y, sqa = qa.x + qa.y, skb = kb.x + kb.y, sqb = qb.x + qb.y;
 #pragma unroll
       for (int o = 1; o < 8; o <<= 1) {
         ska += __shfl_xor_sync(0xffffffffu, ska, o);
@@ -244,11 +240,11 @@ __global__ void __launch_bounds__(kDelThreads) delta_recurrence_kernel(DeltaArgs
         sqb += __shfl_xor_sync(0xffffffffu, sqb, o);
       }
       const float ua = beta * (va - g * ska), ub = beta * (vb - g * skb);
-      const uint64_t ua2 = f2_pack(ua, ua), ub2 = f2_pack(ub, ub), g2 = f2_pack(g, g);
+      const float2 ua2 = make_float2(ua, ua), ub2 = make_float2(ub, ub), g2 = make_float2(g, g);
 #pragma unroll
       for (int i = 0; i < CPL / 2; ++i) {
-        Sa[i] = f2_fma(kk[i], ua2, f2_mul(g2, Sa[i]));
-        Sb[i] = f2_fma(kk[i], ub2, f2_mul(g2, Sb[i]));
+        Sa[i] = __ffma2_rn(kk[i], ua2, __fmul2_rn(g2, Sa[i]));
+        Sb[i] = __ffma2_rn(kk[i], ub2, __fmul2_rn(g2, Sb[i]));
       }
       if (sub == 0) {
         obuf[tt * 32 + col] = fmaf(kq, ua, g * sqa);
@@ -267,13 +263,10 @@ __global__ void __launch_bounds__(kDelThreads) delta_recurrence_kernel(DeltaArgs
 #pragma unroll
     for (int e = 0; e < 2; ++e) {
       const int ch = 4 * (sub + 8 * i) + 2 * e;
-      float s0, s1;
-      f2_unpack(Sa[2 * i + e], s0, s1);
-      if (live0 && ch < D) st[(size_t)ch * a.Dv + j0] = s0;
-      if (live0 && ch + 1 < D) st[(size_t)(ch + 1) * a.Dv + j0] = s1;
-      f2_unpack(Sb[2 * i + e], s0, s1);
-      if (live1 && ch < D) st[(size_t)ch * a.Dv + j1] = s0;
-      if (live1 && ch + 1 < D) st[(size_t)(ch + 1) * a.Dv + j1] = s1;
+      if (live0 && ch < D) st[(size_t)ch * a.Dv + j0] = Sa[2 * i + e].x;
+      if (live0 && ch + 1 < D) st[(size_t)(ch + 1) * a.Dv + j0] = Sa[2 * i + e].y;
+      if (live1 && ch < D) st[(size_t)ch * a.Dv + j1] = Sb[2 * i + e].x;
+      if (live1 && ch + 1 < D) st[(size_t)(ch + 1) * a.Dv + j1] = Sb[2 * i + e].y;
     }
 }
 

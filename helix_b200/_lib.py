@@ -37,14 +37,17 @@ class LayerDescC(C.Structure):
                 ("identity_experts", C.c_int32), ("top_k", C.c_int32), ("score_cap", C.c_float), ("conv_taps", C.c_int32),
                 ("router_kind", C.c_int32), ("route_groups", C.c_int32), ("route_keep", C.c_int32), ("route_renorm", C.c_int32),
                 ("route_scale", C.c_float), ("expert_kind", C.c_int32), ("shared_ff", C.c_int32), ("shared_limit", C.c_float),
-                ("reserved", C.c_int32 * 6)]
+                ("weights_of", C.c_int32), ("rope_linear", C.c_float), ("norm_groups", C.c_int32), ("gate_cap", C.c_float),
+                ("side_mixer", C.c_int32), ("side_heads", C.c_int32), ("side_dim", C.c_int32), ("side_vdim", C.c_int32),
+                ("side_gate_cap", C.c_float), ("mix_scale", C.c_float), ("side_scale", C.c_float),
+                ("reserved", C.c_int32 * 5)]
 
 
 class StackDescC(C.Structure):
     _fields_ = [("width", C.c_int32), ("vocab", C.c_int32), ("n_layers", C.c_int32), ("compute_f32", C.c_int32),
                 ("norm_eps", C.c_float), ("resid_alpha", C.c_float), ("logit_softcap", C.c_float), ("norm_place", C.c_int32),
                 ("embed_norm", C.c_int32), ("plain_gains", C.c_int32), ("norm_kind", C.c_int32), ("embed_scale", C.c_float),
-                ("logit_scale", C.c_float), ("reserved", C.c_int32 * 5)]
+                ("logit_scale", C.c_float), ("tie_head", C.c_int32), ("reserved", C.c_int32 * 4)]
 
 
 class SeqFeedC(C.Structure):

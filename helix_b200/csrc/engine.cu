@@ -288,13 +288,14 @@ int Engine::tensor_set(const char* name, const void* host, size_t n) {
   const Placement& p = it->second;
   if (n != p.rows * p.cols) return fail(HB_ERR_INVALID, std::string("tensor size mismatch for ") + name);
   CU(cudaSetDevice(cfg_.device));
+  const size_t ld = p.ld ? p.ld : p.cols;  // rows of the destination may lie apart (two tensors side by side in every row)
   if (p.elem == 4) {  // fp32 arena: bf16 payloads are widened (exactly) on the way in
     std::vector<uint32_t> wide(n);
     const uint16_t* src = static_cast<const uint16_t*>(host);
     for (size_t i = 0; i < n; ++i) wide[i] = (uint32_t)src[i] << 16;
-    CU(cudaMemcpy(p.dst, wide.data(), n * 4, cudaMemcpyHostToDevice));
+    CU(cudaMemcpy2D(p.dst, ld * 4, wide.data(), p.cols * 4, p.cols * 4, p.rows, cudaMemcpyHostToDevice));
   } else if (p.mode == 0) {
-    CU(cudaMemcpy(p.dst, host, n * 2, cudaMemcpyHostToDevice));
+    CU(cudaMemcpy2D(p.dst, ld * 2, host, p.cols * 2, p.cols * 2, p.rows, cudaMemcpyHostToDevice));
   } else {
     // gate (mode 1) / up (mode 2) rows interleaved per 128-row block: block t -> rows [t*256 + (mode-1)*128, +128)
     const size_t blocks = p.rows / 128;

@@ -191,7 +191,12 @@ class Engine {
     float *x, *p1, *p2, *cq, *qabs, *ctx, *mo, *y;
     bf16 *x16, *cq16, *mo16;
     float* hn = nullptr;      // HB_NORM_BOTH_SIDES: the normed input of the current sublayer [T][width] (x16 is then ITS bf16 copy)
-    float* y2 = nullptr;      // mixture of experts with a unit every token uses: that unit's output [T][width]
+    float* y2 = nullptr;      // mixture of experts with a unit every token uses: that unit's output [T][width]; HB_NORM_PARALLEL: the feed-forward's
+    float* hn2 = nullptr;     // HB_NORM_PARALLEL: the normed input of the feed-forward [T][width] and its bf16 copy (hn / x16: the mixer's)
+    bf16* x16b = nullptr;
+    float* cv = nullptr;      // convolved rows [T][ldcv] (state-space layers; grouped-query layers with convolved projections)
+    float* ab = nullptr;      // scalar-decay recurrences: [T][ldab] = decay (H) | input weight (H) | exp(-m) (H) | n . q (H)
+    int ldcv = 0, ldab = 0, ab_heads = 0;
     float* vfirst = nullptr;  // blended values: the first blending layer's values of the step's tokens [T][kv_heads * vdim]
     int ld1, ld2, ldcq, ldqa, ldctx, ldmo;
     // attention of long prompt portions as dense products (bf16 mode): bf16 queries, gathered keys, scores, probabilities

@@ -23,6 +23,11 @@
 //     sigmoid router with an optional restriction to the best groups of experts, choice in fp32, items sorted by expert into
 //     128-row segments on the device, two grouped tcgen05 products, an optional unit every token uses; nothing returns to the
 //     host, so decode graphs stay static).
+//   * stacks whose two sublayers read the same stream (x <- x + mixer(norm1 x) + ff(norm2 x)): one launch adds both outputs and
+//     forms both normed inputs of the next layer from one row statistic; state-space layers and matrix memories (scalar-decay
+//     recurrences on one kernel, state and convolution inputs in the slot); a second mixer beside a grouped-query one, their
+//     output projections as one product over the concatenated inputs; layers that use an earlier layer's tensors with planes
+//     and state of their own; logits from the embedding table.
 #include "engine.h"
 #include "launch.h"
 
@@ -43,13 +48,14 @@ __device__ __forceinline__ uint64_t mix64(uint64_t z) {
   return z ^ (z >> 31);
 }
 template <typename T>
-__global__ void fill_uniform_kernel(T* p, size_t n, uint64_t seed, float amp, float mean) {
+__global__ void fill_uniform_kernel(T* p, size_t n, uint64_t seed, float amp, float mean, size_t cols, size_t ld) {
   const size_t stride = (size_t)gridDim.x * blockDim.x;
   for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
     const uint64_t h = mix64(seed ^ (i * 0xD1B54A32D192ED03ull));
     const float u = (float)(h >> 40) * (1.0f / 16777216.0f) * 2.0f - 1.0f;
     const float v = __bfloat162float(__float2bfloat16(u * amp + mean));  // bf16-representable in either mode
-    if constexpr (sizeof(T) == 4) p[i] = v; else p[i] = __float2bfloat16(v);
+    const size_t at = ld == cols ? i : i / cols * ld + i % cols;         // rows of `cols` elements, `ld` apart
+    if constexpr (sizeof(T) == 4) p[at] = v; else p[at] = __float2bfloat16(v);
   }
 }
 }  // namespace
@@ -131,8 +137,9 @@ int Engine::load_random_stack(const hb_stack_desc& sd, const hb_layer_desc* laye
     // [128 gate | 128 up] tiles: the gate and up placements share a base; random values need no interleaving, the up
     // tensor's share of the block is simply its second half
     bf16* dst = p.dst + (p.mode == 2 ? n : 0);
-    if (p.elem == 4) fill_uniform_kernel<float><<<148 * 4, 256, 0, stream_>>>((float*)p.dst, n, sk, amp, mean);
-    else fill_uniform_kernel<bf16><<<148 * 4, 256, 0, stream_>>>(dst, n, sk, amp, mean);
+    const size_t ld = p.ld ? p.ld : p.cols;
+    if (p.elem == 4) fill_uniform_kernel<float><<<148 * 4, 256, 0, stream_>>>((float*)p.dst, n, sk, amp, mean, p.cols, ld);
+    else fill_uniform_kernel<bf16><<<148 * 4, 256, 0, stream_>>>(dst, n, sk, amp, mean, p.cols, ld);
     CU(cudaGetLastError());
     model_.filled[kv.first] = true;
   }
@@ -153,7 +160,8 @@ static size_t stack_skinny_floats(const Model& m) {
   for (int i = 0; i < m.sd.n_layers; ++i) {
     const hb_layer_desc& l = m.sl[i];
     shape(m.sw[i].n_in, W);
-    shape(W, (size_t)l.heads * l.vdim);
+    shape(W, m.sw[i].o_cols ? (size_t)m.sw[i].o_cols : (size_t)l.heads * l.vdim);
+    if (l.ff > 0 && l.ff_kind == HB_FF_RELU2) shape(l.ff, W);
     if (l.mixer == HB_MIXER_LATENT) shape((size_t)l.heads * (l.dim + l.rot_dim), l.q_rank);
     if (l.ff > 0) {
       shape(2 * (size_t)l.ff, W);
@@ -204,6 +212,8 @@ struct StackDims {
   int moe_e = 0, moe_f = 0;  // grouped tensor-core experts: most experts / widest expert over the layers that qualify
   int vf = 0;                // layers that blend values: kv_heads * vdim
   bool shared = false;       // some mixture has a unit every token uses
+  int cv = 0;                // widest convolved row (state-space layers, grouped-query layers with convolved projections)
+  int ab = 0;                // most heads of a scalar-decay recurrence (decay, input weight, exp(-m), n . q per head and token)
 };
 // Grouped-query layers whose prompt portions run on the fused tcgen05 attention kernel (the one the Llama path uses, with
 // the mask — blocks, a sliding window or plain causal —, the score cap and the sinks of the denominator as parameters): bf16
@@ -231,7 +241,18 @@ static StackDims stack_dims(const Model& m, int max_ctx) {
       d.gu = std::max(d.gu, 2 * l.shared_ff);
       d.shared = true;
     }
-    if (l.mixer == HB_MIXER_DELTA) {
+    d.mo = std::max(d.mo, m.sw[i].o_cols);
+    if (l.ff > 0 && l.ff_kind == HB_FF_RELU2) d.gu = std::max(d.gu, l.ff);
+    if (m.sw[i].ml.H > 0) {
+      d.cx = std::max(d.cx, m.sw[i].ml.H * m.sw[i].ml.Dv);
+      d.ab = std::max(d.ab, m.sw[i].ml.H);
+    }
+    if (l.mixer == HB_MIXER_MAMBA2) {
+      d.cx = std::max(d.cx, l.heads * l.vdim);
+      d.cv = std::max(d.cv, l.heads * l.vdim + 2 * l.kv_heads * l.dim);
+      d.ab = std::max(d.ab, l.heads);
+    } else if (l.mixer == HB_MIXER_MLSTM) {
+    } else if (l.mixer == HB_MIXER_DELTA) {
       d.n2 = std::max(d.n2, 2 * l.kv_heads * l.dim + l.heads * l.vdim + 2 * l.heads + l.kv_heads);
       d.cx = std::max(d.cx, l.heads * l.vdim);
     } else if (l.mixer == HB_MIXER_GLA) {
@@ -240,6 +261,8 @@ static StackDims stack_dims(const Model& m, int max_ctx) {
     } else if (l.mixer == HB_MIXER_GQA) {
       d.n2 = std::max(d.n2, l.heads * l.dim);
       d.rope_half += l.rope_dims / 2;
+      if (l.attn_flags & HB_ATTN_QKV_CONV) d.cv = std::max(d.cv, (l.heads + l.kv_heads) * l.dim + l.kv_heads * l.vdim);
+      if ((l.attn_flags & HB_ATTN_OUT_GATE) || l.side_heads > 0) d.cx = std::max(d.cx, l.heads * l.vdim);
       if (l.attn_flags & HB_ATTN_V_BLEND) d.vf = std::max(d.vf, l.kv_heads * l.vdim);
       if (gqa_fused_ok(m, l, max_ctx)) {
         d.att = std::max(d.att, l.heads * l.vdim);
@@ -285,8 +308,10 @@ size_t Engine::workspace_bytes_stack() const {
     b += al256(std::max(T * (size_t)up8(dm.gu), rows * 2 * (size_t)dm.moe_f) * 2 + 256);
   }
   b += 2 * al256(T * W * 4) + al256(T * W * 2);                       // x, y, x16
-  if (sd.norm_place == HB_NORM_BOTH_SIDES) b += al256(T * W * 4);     // hn
-  if (dm.shared) b += al256(T * W * 4);                               // y2
+  if (sd.norm_place == HB_NORM_BOTH_SIDES || sd.norm_place == HB_NORM_PARALLEL) b += al256(T * W * 4);     // hn
+  if (sd.norm_place == HB_NORM_PARALLEL) b += al256(T * W * 4) + al256(T * W * 2);  // hn2, x16b
+  if (dm.shared || sd.norm_place == HB_NORM_PARALLEL) b += al256(T * W * 4);                               // y2
+  b += al256(T * (size_t)up8(dm.cv) * 4) + al256(T * (size_t)up8(4 * dm.ab) * 4);  // cv, ab
   if (dm.vf > 0) b += al256(T * (size_t)dm.vf * 4);                   // vfirst
   b += al256(T * (size_t)up8(n1) * 4) + al256(T * (size_t)up8(n2) * 4);  // p1, p2
   b += al256(T * (size_t)up8(q) * 4) + al256(T * (size_t)up8(q) * 2);     // cq, cq16
@@ -312,13 +337,15 @@ int Engine::alloc_runtime_stack() {
   CU(stack_gqa_init());
   CU(stack_moe_init());
   CU(stack_delta_init());
+  CU(stack_ssm_init());
   if (!sd.compute_f32) {  // stream-K plans allocate on first use of a shape: make them now, not inside a graph capture
     SmLimitScope sm_scope(cfg_.sm_budget);
     SkinnyPlan pl{};
     for (int i = 0; i < sd.n_layers; ++i) {
       const hb_layer_desc& l = model_.sl[i];
       CU(gemm_skinny_plan(model_.sw[i].n_in, sd.width, &pl));
-      CU(gemm_skinny_plan(sd.width, l.heads * l.vdim, &pl));
+      CU(gemm_skinny_plan(sd.width, model_.sw[i].o_cols ? model_.sw[i].o_cols : l.heads * l.vdim, &pl));
+      if (l.ff > 0 && l.ff_kind == HB_FF_RELU2) CU(gemm_skinny_plan(l.ff, sd.width, &pl));
       if (l.mixer == HB_MIXER_LATENT) CU(gemm_skinny_plan(l.heads * (l.dim + l.rot_dim), l.q_rank, &pl));
       if (l.ff > 0) {
         CU(gemm_skinny_plan(2 * l.ff, sd.width, &pl));
@@ -400,8 +427,14 @@ int Engine::alloc_runtime_stack() {
   sk_.x = (float*)take(T * W * 4);
   sk_.y = (float*)take(T * W * 4);
   sk_.x16 = (bf16*)take(T * W * 2);
-  sk_.hn = sd.norm_place == HB_NORM_BOTH_SIDES ? (float*)take(T * W * 4) : nullptr;
-  sk_.y2 = dm.shared ? (float*)take(T * W * 4) : nullptr;
+  const bool par = sd.norm_place == HB_NORM_PARALLEL;
+  sk_.hn = (sd.norm_place == HB_NORM_BOTH_SIDES || par) ? (float*)take(T * W * 4) : nullptr;
+  sk_.hn2 = par ? (float*)take(T * W * 4) : nullptr;
+  sk_.x16b = par ? (bf16*)take(T * W * 2) : nullptr;
+  sk_.y2 = (dm.shared || par) ? (float*)take(T * W * 4) : nullptr;
+  sk_.ldcv = up8(dm.cv); sk_.ldab = up8(4 * dm.ab); sk_.ab_heads = dm.ab;
+  sk_.cv = (float*)take(T * (size_t)sk_.ldcv * 4);
+  sk_.ab = (float*)take(T * (size_t)sk_.ldab * 4);
   sk_.vfirst = dm.vf > 0 ? (float*)take(T * (size_t)dm.vf * 4) : nullptr;
   sk_.p1 = (float*)take(T * (size_t)sk_.ld1 * 4);
   sk_.p2 = (float*)take(T * (size_t)sk_.ld2 * 4);
@@ -552,8 +585,19 @@ int Engine::forward_stack(int T, int B, const StepLayout& L, const int32_t* extr
 
   const float goff = sd.plain_gains ? 0.f : 1.f;  // stored norm gains are offsets from one unless plain
   const bool both = sd.norm_place == HB_NORM_BOTH_SIDES, tnorm = sd.norm_kind == HB_NORM_TANH;
-  // what a sublayer reads: the stream itself, or (norms on both sides) its normed copy; x16 is the bf16 copy of that
-  const float* xin = both ? k.hn : k.x;
+  const bool par = sd.norm_place == HB_NORM_PARALLEL;
+  // what a sublayer reads: the stream itself, or (norms on both sides, parallel sublayers) its normed copy; x16 is the bf16
+  // copy of that.  With parallel sublayers the feed-forward has a normed copy of its own (hn2 / x16b).
+  const float* xin = (both || par) ? k.hn : k.x;
+  const float* ff_in = par ? k.hn2 : xin;
+  const bf16* ff_in16 = par ? (f32 ? nullptr : k.x16b) : x16;
+  // parallel sublayers: x += mixer + feed-forward (+ bias), and the two normed inputs of the layer `next` (none behind the last)
+  auto par_step = [&](const float* y, const float* y2, const void* bias, float bias_scale, int next) -> cudaError_t {
+    const void* w1 = next < sd.n_layers ? model_.sw[next].norm1 : nullptr;
+    const void* w2 = next < sd.n_layers && model_.sl[next].ff > 0 ? model_.sw[next].norm2 : nullptr;
+    return parallel_step(stream_, k.x, nullptr, y, y2, bias, bias_scale, w1, w2, f32, sd.norm_eps, y ? k.x : nullptr, k.hn, x16, k.hn2,
+                         f32 ? nullptr : k.x16b, T, W);
+  };
   // the residual step: the norm covers the sum (post-norm stream) or the sublayer's output alone; with norms on both sides
   // the same launch also norms the input of the sublayer that follows (`pre`, null behind the last one)
   auto resid = [&](const void* bias, const void* gain, const void* pre) -> cudaError_t {
@@ -583,25 +627,65 @@ int Engine::forward_stack(int T, int B, const StepLayout& L, const int32_t* extr
     int rc;
     if (T > 256 && k.gu16 && F % 8 == 0 && stack_tc(2 * F, W, W, W) && stack_tc(W, F, F, W)) {
       if (packed) {
-        GemmArgs g{x16, W, (const bf16*)w_gu, W, mo16, F, nullptr, 0, nullptr, T, 2 * F, W,
+        GemmArgs g{ff_in16, W, (const bf16*)w_gu, W, mo16, F, nullptr, 0, nullptr, T, 2 * F, W,
                    act == GLU_GELU_TANH ? EPI_GEGLU : (act == GLU_CLAMPED ? EPI_CLAMPGLU : EPI_SWIGLU), 0};
         g.glu_limit = limit;
         SPAN(0, 4.0 * T * F * W, gemm_bf16_tn(stream_, g));
       } else {
-        GemmArgs g{x16, W, (const bf16*)w_gu, W, k.gu16, 2 * F, nullptr, 0, nullptr, T, 2 * F, W, EPI_NONE, 0};
+        GemmArgs g{ff_in16, W, (const bf16*)w_gu, W, k.gu16, 2 * F, nullptr, 0, nullptr, T, 2 * F, W, EPI_NONE, 0};
         SPAN(0, 4.0 * T * F * W, gemm_bf16_tn(stream_, g));
         SPAN(3, 6.0 * T * F, gated_unit_b16(stream_, k.gu16, 2 * F, act, mo16, T, F, limit));
       }
     } else {
-      rc = stack_gemm(xin, x16, W, w_gu, 2 * F, W, k.p1, k.ld1, T);
+      rc = stack_gemm(ff_in, ff_in16, W, w_gu, 2 * F, W, k.p1, k.ld1, T);
       if (rc != HB_OK) return rc;
       SPAN(3, 12.0 * T * F, gated_unit(stream_, k.p1, k.ld1, act, k.mo, mo16, T, F, packed, limit));
     }
     return stack_gemm(k.mo, mo16, F, w_down, W, F, out, W, T);
   };
+  // ungated unit y = down(relu(up h)^2)
+  auto relu2_ff = [&](const void* w_up, const void* w_down, int F, float* out) -> int {
+    if (T > 256 && k.gu16 && F % 8 == 0 && stack_tc(F, W, W, F) && stack_tc(W, F, F, W)) {
+      GemmArgs g{ff_in16, W, (const bf16*)w_up, W, mo16, F, nullptr, 0, nullptr, T, F, W, EPI_RELU2, 0};
+      SPAN(0, 2.0 * T * F * W, gemm_bf16_tn(stream_, g));
+    } else {
+      int rc = stack_gemm(ff_in, ff_in16, W, w_up, F, W, k.p1, k.ld1, T);
+      if (rc != HB_OK) return rc;
+      SPAN(3, 10.0 * T * F, relu2_rows(stream_, k.p1, k.ld1, k.mo, mo16, T, F));
+    }
+    return stack_gemm(k.mo, mo16, F, w_down, W, F, out, W, T);
+  };
+  // a matrix memory over the columns of the layer's fused projection (row stride ldin): gates and their running maximum,
+  // the recurrence, then normalisation, per-head unit RMS, gain, sigmoid gate and `scale` into columns col0.. of the output
+  // projection's input (row stride ldout)
+  auto run_memory = [&](const StackLayerW& w, int ldin, int col0, int ldout, float scale) -> int {
+    const MlstmW& q = w.ml;
+    GateScanArgs ga{};
+    ga.p = k.p1; ga.ldp = ldin; ga.off_i = q.off_i; ga.off_f = q.off_f; ga.bias = w.b_in; ga.f32 = f32; ga.cap = q.cap;
+    ga.ab = k.ab; ga.ldab = k.ldab;
+    ga.state = state_; ga.slot_stride = (long)model_.state_floats; ga.m_off = q.m_off;
+    ga.cu = cu; ga.first_pos = first; ga.slots = sslot; ga.B = B; ga.H = q.H;
+    SPAN(3, 24.0 * T * q.H, exp_gate_scan(stream_, ga));
+    LinRecArgs ra{};
+    ra.q = k.p1; ra.ldq = ldin; ra.q_off = q.off_q;
+    ra.k = k.p1; ra.ldk = ldin; ra.k_off = q.off_k;
+    ra.v = k.p1; ra.ldv = ldin; ra.v_off = q.off_v;
+    ra.ab = k.ab; ra.ldab = k.ldab;
+    ra.out = k.ctx; ra.ldo = k.ldctx;
+    ra.nq = k.ab + 3 * q.H; ra.ldn = k.ldab;
+    ra.skip = nullptr; ra.f32 = f32; ra.q_scale = 1.0f / sqrtf((float)q.D);
+    ra.state = state_; ra.slot_stride = (long)model_.state_floats; ra.s_off = q.state_off; ra.n_off = q.n_off;
+    ra.cu = cu; ra.first_pos = first; ra.slots = sslot;
+    ra.B = B; ra.H = q.H; ra.G = q.H; ra.Dk = q.D; ra.Dv = q.Dv;
+    SPAN(6, 4.0 * T * q.H * q.D * q.Dv, lin_recurrence(stream_, ra));
+    SPAN(3, 16.0 * T * q.H * q.Dv, memory_readout(stream_, k.ctx, k.ldctx, k.ab + 3 * q.H, k.ldab, k.ab, k.ldab, k.p1 + q.off_g, ldin, q.hnorm, f32,
+                                                  sd.norm_eps, scale, k.mo, mo16, ldout, col0, T, q.H, q.Dv));
+    return HB_OK;
+  };
   SPAN(3, rowb, embed_rows_f32(stream_, tokens, model_.s_embed, f32, k.x, x16, T, W, sd.embed_scale != 0.f ? sd.embed_scale : 1.f));
   if (sd.embed_norm) SPAN(3, 2 * rowb, norm_rows(k.x, nullptr, model_.s_embed_norm, k.x, both ? nullptr : x16, T));
   if (both) SPAN(3, 2 * rowb, norm_rows(k.x, nullptr, model_.sw[0].norm1, k.hn, x16, T));
+  if (par) SPAN(3, 3 * rowb, par_step(nullptr, nullptr, nullptr, 0.f, 0));
   for (size_t si = 0; si < k.freq_sets.size(); ++si)  // cos / sin of the step's positions, once per distinct rotation
     SPAN(3, 8.0 * T * k.freq_half[si], stack_rope_table(stream_, positions, k.freq_sets[si], k.freq_half[si], k.rope_cs[si], T));
   for (int i = 0; i < sd.n_layers; ++i) {
@@ -615,7 +699,36 @@ int Engine::forward_stack(int T, int B, const StepLayout& L, const int32_t* extr
     if (rc != HB_OK) return rc;
     // the norm that prepares the input of whatever follows a sublayer (norms on both sides)
     const void* pre_next = i + 1 < sd.n_layers ? model_.sw[i + 1].norm1 : nullptr;
-    if (l.mixer == HB_MIXER_DELTA) {
+    const int ocols = w.o_cols ? w.o_cols : H * Dv;  // columns of the output projection (both mixers' when there are two)
+    if (l.mixer == HB_MIXER_MAMBA2) {
+      const int G = l.kv_heads, N = Dk, inner = H * Dv, C = inner + 2 * G * N;
+      ConvArgs ca{};
+      ca.in = k.p1; ca.ldi = k.ld1; ca.off = w.off_v; ca.in_bias = nullptr; ca.bias_off = 0;
+      ca.w = w.conv_w; ca.bias = w.conv_b; ca.f32 = f32; ca.taps = l.conv_taps; ca.act = 1;
+      ca.out = k.cv; ca.ldo = k.ldcv;
+      ca.state = state_; ca.slot_stride = (long)model_.state_floats; ca.tail_off = w.tail_off;
+      ca.cu = cu; ca.first_pos = first; ca.slots = sslot; ca.seq_of = seqof; ca.T = T; ca.B = B; ca.C = C;
+      SPAN(3, 4.0 * T * C * (l.conv_taps + 1), short_conv(stream_, ca));
+      SPAN(3, 8.0 * B * C * l.conv_taps, conv_tails(stream_, ca));
+      SPAN(3, 12.0 * T * H, ssm_steps(stream_, k.p1, k.ld1, w.off_a, w.a_dt, f32, k.ab, k.ldab, T, H));
+      LinRecArgs ra{};
+      ra.q = k.cv; ra.ldq = k.ldcv; ra.q_off = inner + G * N;
+      ra.k = k.cv; ra.ldk = k.ldcv; ra.k_off = inner;
+      ra.v = k.cv; ra.ldv = k.ldcv; ra.v_off = 0;
+      ra.ab = k.ab; ra.ldab = k.ldab;
+      ra.out = k.ctx; ra.ldo = k.ldctx;
+      ra.nq = nullptr; ra.ldn = 0;
+      ra.skip = (const uint8_t*)w.a_dt + (size_t)2 * H * model_.elem; ra.f32 = f32; ra.q_scale = 1.f;
+      ra.state = state_; ra.slot_stride = (long)model_.state_floats; ra.s_off = w.state_off; ra.n_off = 0;
+      ra.cu = cu; ra.first_pos = first; ra.slots = sslot;
+      ra.B = B; ra.H = H; ra.G = G; ra.Dk = N; ra.Dv = Dv;
+      SPAN(6, 4.0 * T * H * N * Dv, lin_recurrence(stream_, ra));
+      SPAN(3, 16.0 * T * inner, gated_group_norm(stream_, k.ctx, k.ldctx, k.p1 + w.off_g, k.ld1, w.hnorm, f32, sd.norm_eps, l.norm_groups, k.mo,
+                                                 mo16, T, inner));
+    } else if (l.mixer == HB_MIXER_MLSTM) {
+      rc = run_memory(w, k.ld1, 0, ocols, 1.f);
+      if (rc != HB_OK) return rc;
+    } else if (l.mixer == HB_MIXER_DELTA) {
       const int G = l.kv_heads, GD = G * Dk, C = 2 * GD + H * Dv;
       DeltaPrepArgs pa{};
       pa.p = k.p1; pa.ldp = k.ld1; pa.off_qkv = w.off_q; pa.off_b = w.off_b; pa.off_a = w.off_a;
@@ -656,6 +769,25 @@ int Engine::forward_stack(int T, int B, const StepLayout& L, const int32_t* extr
       void* vplane = (uint8_t*)kv_ + plane_off_[w.cache_plane_v];
       GqaPrepArgs pa{};
       pa.p = k.p1; pa.ldp = ldin; pa.q_off = w.off_q; pa.k_off = w.off_k; pa.v_off = w.off_v;
+      const bool conv = (l.attn_flags & HB_ATTN_QKV_CONV) != 0;
+      if (conv) {
+        // q | k | v columns (biases added on the way in) through their short convolutions; what follows reads the convolved rows
+        const int C = (H + G) * Dk + G * Dv;
+        ConvArgs ca{};
+        ca.in = k.p1; ca.ldi = ldin; ca.off = w.off_q;
+        ca.in_bias = (l.attn_flags & HB_ATTN_QKV_BIAS) ? w.b_in : nullptr; ca.bias_off = w.off_q;
+        ca.w = w.conv_w; ca.bias = nullptr; ca.f32 = f32; ca.taps = l.conv_taps; ca.act = 0;
+        ca.out = k.cv; ca.ldo = k.ldcv;
+        ca.state = state_; ca.slot_stride = (long)model_.state_floats; ca.tail_off = w.tail_off;
+        ca.cu = cu; ca.first_pos = first; ca.slots = sslot; ca.seq_of = seqof; ca.T = T; ca.B = B; ca.C = C;
+        SPAN(3, 4.0 * T * C * (l.conv_taps + 1), short_conv(stream_, ca));
+        SPAN(3, 8.0 * B * C * l.conv_taps, conv_tails(stream_, ca));
+        pa.p = k.cv; pa.ldp = k.ldcv; pa.q_off = 0; pa.k_off = H * Dk; pa.v_off = (H + G) * Dk;
+      }
+      // an entry-wise output gate or a second mixer: the attention output passes one more kernel on its way to the output
+      // projection's input (gate, weight of the mixer, its columns of the concatenated row)
+      const bool post = (l.attn_flags & HB_ATTN_OUT_GATE) || w.ml.H > 0;
+      const float mix_scale = l.mix_scale != 0.f ? l.mix_scale : 1.f;
       // prompt portions (any entry of >= kAttDenseMin tokens): the whole step runs on the fused tcgen05 kernel over the paged
       // planes; steps of single tokens and short portions, other masks, head sizes and the exact mode take the per-token kernel
       bool fused = gqa_fused_ok(model_, l, cfg_.max_ctx) && k.att16 && k.q16 && (H * Dk) % 8 == 0 && page_ == 64;
@@ -674,7 +806,7 @@ int Engine::forward_stack(int T, int B, const StepLayout& L, const int32_t* extr
       pa.cs = k.layer_set[i] >= 0 ? k.rope_cs[k.layer_set[i]] : nullptr; pa.rope_dims = l.rope_dims; pa.pairing = l.rope_pairing;
       pa.H = H; pa.G = G; pa.D = Dk; pa.Dv = Dv; pa.page_size = page_;
       pa.unit_norm = (l.attn_flags & HB_ATTN_QK_UNIT_NORM) != 0; pa.eps = sd.norm_eps; pa.T = T;
-      pa.bias = (l.attn_flags & HB_ATTN_QKV_BIAS) ? w.b_in : nullptr;
+      pa.bias = ((l.attn_flags & HB_ATTN_QKV_BIAS) && !conv) ? w.b_in : nullptr;
       pa.proj_norm = (l.attn_flags & HB_ATTN_QK_PROJ_NORM) != 0; pa.qk_gain = w.qk_gain;
       pa.blend_role = w.blend_role; pa.vmix = w.vmix; pa.v_first = k.vfirst;
       SPAN(3, 8.0 * T * (H + 2 * G) * Dk, gqa_prep(stream_, pa));
@@ -684,7 +816,7 @@ int Engine::forward_stack(int T, int B, const StepLayout& L, const int32_t* extr
         da.k_cache = (const bf16*)kplane; da.v_cache = (const bf16*)vplane;
         da.page_table = pt; da.max_pages = max_pages_per_seq_;
         da.ctx_lens = (const int32_t*)(d_step_ + L.ctx);
-        da.out = mo16; da.ldo = H * Dv;
+        da.out = post ? k.att16 : mo16; da.ldo = H * Dv;
         da.workspace = k.dec_ws;
         da.B = B; da.Hq = H; da.Hkv = G; da.D = Dk; da.page_size = page_;
         const int want = (int)(0.8 * 2 * (cfg_.sm_budget > 0 ? cfg_.sm_budget : 148));
@@ -701,7 +833,7 @@ int Engine::forward_stack(int T, int B, const StepLayout& L, const int32_t* extr
         AttnPrefillArgs fa{};
         fa.q = k.q16; fa.ldq = H * Dk;
         fa.k = nullptr; fa.ldk = 0; fa.v = nullptr; fa.ldv = 0;
-        const bool direct = stack_tc(W, H * Dv, H * Dv, W);  // the output projection reads the bf16 copy only
+        const bool direct = !post && stack_tc(W, H * Dv, H * Dv, W);  // the output projection reads the bf16 copy only
         fa.out = direct ? mo16 : k.att16; fa.ldo = H * Dv;
         if (direct && (l.attn_flags & HB_ATTN_HEAD_GATE)) { fa.head_gate = k.p1 + w.off_g; fa.ldg = ldin; }
         fa.cu_seqlens = cu; fa.B = B; fa.T = T; fa.max_seqlen = longest;
@@ -714,7 +846,7 @@ int Engine::forward_stack(int T, int B, const StepLayout& L, const int32_t* extr
         fa.softcap = l.score_cap; fa.sink = (l.attn_flags & HB_ATTN_LEARNED_SINK) ? (const bf16*)w.sink : nullptr;
         fa.unit_sink = (l.attn_flags & HB_ATTN_UNIT_SINK) ? 1 : 0;
         SPAN(1, 2.0 * T * H * (double)std::min(l.window, cfg_.max_ctx) * (Dk + Dv) * 0.5, attn_prefill(stream_, fa));
-        if (!direct)
+        if (!direct && !post)
           SPAN(3, 10.0 * T * H * Dv, head_gate_rows(stream_, k.att16, H * Dv, (l.attn_flags & HB_ATTN_HEAD_GATE) ? k.p1 + w.off_g : nullptr,
                                                     ldin, k.mo, mo16, T, H, Dv));
       } else {
@@ -724,11 +856,23 @@ int Engine::forward_stack(int T, int B, const StepLayout& L, const int32_t* extr
       aa.page_table = pt; aa.max_pages = max_pages_per_seq_; aa.page_size = page_;
       aa.positions = positions; aa.seq_of = seqof;
       aa.gate = (l.attn_flags & HB_ATTN_HEAD_GATE) ? k.p1 + w.off_g : nullptr; aa.ldg = ldin;
-      aa.out = k.mo; aa.ldo = H * Dv; aa.out_b16 = mo16;
+      aa.out = post ? k.ctx : k.mo; aa.ldo = H * Dv; aa.out_b16 = post ? nullptr : mo16;
       aa.T = T; aa.H = H; aa.G = G; aa.D = Dk; aa.Dv = Dv; aa.mask = l.mask; aa.window = l.window;
       aa.unit_sink = (l.attn_flags & HB_ATTN_UNIT_SINK) != 0; aa.scale = l.scale;
       aa.softcap = l.score_cap; aa.sink = (l.attn_flags & HB_ATTN_LEARNED_SINK) ? w.sink : nullptr;
       SPAN(7, 2.0 * T * H * (double)std::min(l.window, cfg_.max_ctx) * (Dk + Dv), gqa_attn(stream_, aa));
+      }
+      if (post) {
+        const bool from16 = tc_dec || fused;
+        if (l.attn_flags & HB_ATTN_OUT_GATE)
+          SPAN(3, 12.0 * T * H * Dv, gate_scale_rows(stream_, from16 ? nullptr : k.ctx, from16 ? k.att16 : nullptr, H * Dv, k.p1 + w.off_g, ldin,
+                                                     mix_scale, k.mo, mo16, ocols, 0, T, H * Dv));
+        else
+          return fail(HB_ERR_INVALID, "a second mixer needs the entry-wise output gate on the first");
+        if (w.ml.H > 0) {
+          rc = run_memory(w, ldin, H * Dv, ocols, l.side_scale != 0.f ? l.side_scale : 1.f);
+          if (rc != HB_OK) return rc;
+        }
       }
     } else {
       const int R = l.kv_rank, Dr = l.rot_dim, Q = l.q_rank;
@@ -823,10 +967,27 @@ int Engine::forward_stack(int T, int B, const StepLayout& L, const int32_t* extr
       }
       SPAN(3, 12.0 * T * H * Dv, sigmoid_gate(stream_, ov, ldov, k.p1 + w.off_g, k.ld1, k.mo, mo16, T, H * Dv));
     }
-    rc = stack_gemm(k.mo, mo16, H * Dv, w.wo, W, H * Dv, k.y, W, T);
+    rc = stack_gemm(k.mo, mo16, ocols, w.wo, W, ocols, k.y, W, T);
     if (rc != HB_OK) return rc;
-    SPAN(3, 3 * rowb, resid(nullptr, both ? w.norm1b : w.norm1, l.ff > 0 ? w.norm2 : pre_next));
-    if (l.ff > 0 && l.ff_kind == HB_FF_MOE) {
+    if (par) {
+      // both sublayers read the same stream: the feed-forward runs on its own normed copy, one launch adds both outputs
+      // (and the first mixer's output bias, times that mixer's weight) and norms the next layer's inputs
+      const float* y2 = nullptr;
+      if (l.ff > 0) {
+        if (l.ff_kind == HB_FF_RELU2) rc = relu2_ff(w.w_gu, w.w_down, l.ff, k.y2);
+        else rc = gated_ff(w.w_gu, w.w_down, l.ff, l.ff_kind == HB_FF_SILU ? GLU_SILU : GLU_GELU_TANH, 0.f, w.gu_packed, k.y2);
+        if (rc != HB_OK) return rc;
+        y2 = k.y2;
+      }
+      SPAN(3, 5 * rowb, par_step(k.y, y2, w.o_bias, l.mix_scale != 0.f ? l.mix_scale : 1.f, i + 1));
+      continue;
+    }
+    SPAN(3, 3 * rowb, resid(w.o_bias, both ? w.norm1b : w.norm1, l.ff > 0 ? w.norm2 : pre_next));
+    if (l.ff > 0 && l.ff_kind == HB_FF_RELU2) {
+      rc = relu2_ff(w.w_gu, w.w_down, l.ff, k.y);
+      if (rc != HB_OK) return rc;
+      SPAN(3, 3 * rowb, resid(nullptr, both ? w.norm2b : w.norm2, pre_next));
+    } else if (l.ff > 0 && l.ff_kind == HB_FF_MOE) {
       // router in fp32 on the stream itself; experts per (token, choice); identity outputs and weights in the combination
       const int E = l.experts, R = l.experts + l.identity_experts, F = l.ff;
       RouteOpts ro;

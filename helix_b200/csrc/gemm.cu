@@ -427,6 +427,13 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 #pragma unroll
               for (int j = 0; j < 32; j += 2) gelu_erf2(f[j], f[j + 1]);
             }
+            if constexpr (EPI == EPI_RELU2) {
+#pragma unroll
+              for (int j = 0; j < 32; ++j) {
+                const float r = fmaxf(f[j], 0.f);
+                f[j] = r * r;
+              }
+            }
             if constexpr (kResid) {
               if (h == 0) {
                 mbar_wait(my_resid_bar, resid_phase);
@@ -596,6 +603,7 @@ cudaError_t gemm_init() {
   if ((e = set_attr_epi<EPI_ROPE>()) != cudaSuccess) return e;
   if ((e = set_attr_epi<EPI_GEGLU>()) != cudaSuccess) return e;
   if ((e = set_attr_epi<EPI_CLAMPGLU>()) != cudaSuccess) return e;
+  if ((e = set_attr_epi<EPI_RELU2>()) != cudaSuccess) return e;
   return set_attr_epi<EPI_SWIGLU>();
 }
 
@@ -642,6 +650,7 @@ cudaError_t gemm_bf16_tn(cudaStream_t stream, const GemmArgs& g) {
       return launch_epi<EPI_CLAMPGLU>(stream, h, sms);
     }
     case EPI_F32: return launch_epi<EPI_F32>(stream, g, sms);
+    case EPI_RELU2: return launch_epi<EPI_RELU2>(stream, g, sms);
     case EPI_ROPE: {
       const RopeEpi& r = g.rope;
       if ((g.N % 256) || !r.out || !r.cs || (r.D != 64 && r.D != 128) || g.N != (r.Hq + 2 * r.Hkv) * r.D || (r.ldc % 8)) return cudaErrorInvalidValue;

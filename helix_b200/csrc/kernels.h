@@ -29,6 +29,7 @@ enum Epi : int {
   EPI_GEGLU = 8,       // as EPI_SWIGLU with gelu_tanh(gate_j) * up_j
   EPI_CLAMPGLU = 9,    // as EPI_SWIGLU with g = min(gate_j, limit), u = clamp(up_j, -limit, limit): g sigmoid(1.702 g) (u + 1)
                        // (limit = GemmArgs::glu_limit)
+  EPI_RELU2 = 10,      // C = relu(acc)^2                      (bf16)
   EPI_ROPE = 7,        // fused QKV projection of a decoder: C = bf16(acc [+ bias]) with the q and k heads rotated
                        // (RopeEpi) and the k / v rows also scattered into the paged KV cache
 };
@@ -458,6 +459,82 @@ struct DeltaArgs {
   int B, H, G, D, Dv;
 };
 cudaError_t delta_recurrence(cudaStream_t s, const DeltaArgs& a);
+
+// ---- short convolutions, scalar-decay linear recurrences (state-space layers, matrix memories), sublayers that share one
+//      residual step (stack_ssm.cu).  Step entries as for gla_recurrence.
+cudaError_t stack_ssm_init();
+// Causal convolution over `taps` tokens per channel of C neighbouring columns of a projection buffer:
+//   u_t[c] = in[t, off + c] (+ in_bias[bias_off + c]);  y_t[c] = act(sum_j w[c][j] u_(t - taps + 1 + j)[c] (+ bias[c]))
+// with zeros before position 0; the taps - 1 inputs before an entry come from the slot ([taps - 1][C] at tail_off), and
+// conv_tails (after short_conv of the same step) moves the slot's inputs on by the entry's tokens.  act: 0 none, 1 silu.
+struct ConvArgs {
+  const float* in; long ldi; int off;
+  const void* in_bias; int bias_off;   // weight type, or null
+  const void* w; const void* bias; bool f32;
+  int taps, act;
+  float* out; long ldo;
+  float* state; long slot_stride; size_t tail_off;
+  const int32_t* cu; const int32_t* first_pos; const int32_t* slots; const int32_t* seq_of;
+  int T, B, C;
+};
+cudaError_t short_conv(cudaStream_t s, const ConvArgs& a);
+cudaError_t conv_tails(cudaStream_t s, const ConvArgs& a);
+// State-space step sizes: dt = softplus(p[t, off_dt + h] + dt_bias[h]); ab[t, h] = exp(-exp(A_log[h]) dt), ab[t, H + h] = dt
+// (a_dt = [A_log (H) | dt_bias (H) | ...] of the weight type)
+cudaError_t ssm_steps(cudaStream_t s, const float* p, long ldp, int off_dt, const void* a_dt, bool f32, float* ab, long ldab, int T, int H);
+// Exponential gates of a matrix memory with their running maximum, one warp per (entry, head) scanning the entry's tokens:
+//   i = cap tanh((p[t, off_i + h] + bias[off_i + h]) / cap);  f = logsigmoid(cap tanh((p[t, off_f + h] + bias[off_f + h]) / cap))
+//   m_t = max(f + m_(t-1), i);  ab[t, h] = exp(f + m_(t-1) - m_t);  ab[t, H + h] = exp(i - m_t);  ab[t, 2H + h] = exp(-m_t)
+// m lives in the slot ([H] floats at m_off) and starts at 0 when the entry starts at position 0.
+struct GateScanArgs {
+  const float* p; long ldp; int off_i, off_f;
+  const void* bias; bool f32;   // [.. off_i .. off_f ..] of the weight type, or null
+  float cap;
+  float* ab; long ldab;
+  float* state; long slot_stride; size_t m_off;
+  const int32_t* cu; const int32_t* first_pos; const int32_t* slots;
+  int B, H;
+};
+cudaError_t exp_gate_scan(cudaStream_t s, const GateScanArgs& a);
+// S_t = a_t S_(t-1) + b_t k_t v_t^T;  out_t = q_scale * S_t^T q_t (+ skip[h] v_t) per (entry, head); query / key head of
+// head h: h / (H / G); a_t = ab[t, h], b_t = ab[t, H + h].  With nq: the vector n_t = a_t n_(t-1) + b_t k_t ([H][Dk] at
+// n_off of the slot) is carried too and nq[t, h] = q_scale * n_t . q_t.  S: [H][Dk][Dv] fp32 at s_off of the slot.
+struct LinRecArgs {
+  const float* q; long ldq; int q_off;
+  const float* k; long ldk; int k_off;
+  const float* v; long ldv; int v_off;
+  const float* ab; long ldab;
+  float* out; long ldo;
+  float* nq; long ldn;
+  const void* skip; bool f32;
+  float q_scale;
+  float* state; long slot_stride; size_t s_off, n_off;
+  const int32_t* cu; const int32_t* first_pos; const int32_t* slots;
+  int B, H, G, Dk, Dv;
+};
+cudaError_t lin_recurrence(cudaStream_t s, const LinRecArgs& a);
+// Matrix memory read-out: o = num[t, h, :] / (max(|nq[t, h]|, ab[t, 2H + h]) + 1e-6); out[t, col0 + h Dv + i] =
+// o_i / rms(o) * w[h Dv + i] * sigmoid(g[t, h Dv + i]) * scale (+ bf16 copy at the same place of out_b16)
+cudaError_t memory_readout(cudaStream_t s, const float* num, long ldnum, const float* nq, long ldn, const float* ab, long ldab,
+                           const float* g, long ldg, const void* w, bool f32, float eps, float scale, float* out, bf16* out_b16,
+                           long ldout, int col0, int T, int H, int Dv);
+// State-space read-out: u = y[t, :] * silu(z[t, :]) over n entries, divided by its root mean square in `parts` equal parts,
+// times w; out [T, n] (+ bf16 copy)
+cudaError_t gated_group_norm(cudaStream_t s, const float* y, long ldy, const float* z, long ldz, const void* w, bool f32, float eps,
+                             int parts, float* out, bf16* out_b16, int T, int n);
+// out[t, col0 + e] = in[t, e] * sigmoid(g[t, e]) * scale, e < n (in: fp32, or bf16 when in_b16 is given instead)
+cudaError_t gate_scale_rows(cudaStream_t s, const float* in, const bf16* in_b16, long ldi, const float* g, long ldg, float scale,
+                            float* out, bf16* out_b16, long ldout, int col0, int T, int n);
+// Sublayers that read the same stream and are added in one step:
+//   v = x[row_index ? row_index[r] : r] (+ y[r]) (+ y2[r]) (+ bias_scale * bias);  x_out[r] = v (when given; may be x);
+//   h1[r] = v / rms(v) * w1, h2[r] = v / rms(v) * w2 as fp32 and / or bf16 (each optional): one statistic serves both norms
+cudaError_t parallel_step(cudaStream_t s, const float* x, const int32_t* row_index, const float* y, const float* y2, const void* bias,
+                          float bias_scale, const void* w1, const void* w2, bool f32, float eps, float* x_out, float* h1, bf16* h1_b16,
+                          float* h2, bf16* h2_b16, int rows, int W);
+// out = relu(in)^2 (fp32 in, row stride ldi; fp32 and / or bf16 out, dense rows of n)
+cudaError_t relu2_rows(cudaStream_t s, const float* in, long ldi, float* out, bf16* out_b16, int T, int n);
+// the same on bf16 rows (tensor-core path)
+cudaError_t relu2_rows_b16(cudaStream_t s, const bf16* in, long ldi, bf16* out, int T, int n);
 
 // ---- gated feed-forward units and mixtures of experts (stack_moe.cu).
 cudaError_t stack_moe_init();

@@ -1,6 +1,7 @@
 #include "model.h"
 
 #include <math.h>
+#include <string.h>
 
 #include <algorithm>
 
@@ -209,8 +210,39 @@ std::string validate_stack(const hb_stack_desc& d, const hb_layer_desc* L) {
       if (l.kv_heads <= 0 || l.heads % l.kv_heads) return "heads must be a multiple of kv_heads" + at;
       if (l.dim > 256) return "delta-rule key channels per head > 256 unsupported" + at;
       if (l.conv_taps < 1 || l.conv_taps > 16) return "convolution taps must be 1..16" + at;
+    } else if (l.mixer == HB_MIXER_MAMBA2) {
+      if (l.kv_heads <= 0 || l.heads % l.kv_heads) return "heads must be a multiple of the groups" + at;
+      if (l.dim > 256) return "state size > 256 unsupported" + at;
+      if (l.conv_taps < 1 || l.conv_taps > 16) return "convolution taps must be 1..16" + at;
+      if (l.norm_groups < 1 || (l.heads * l.vdim) % l.norm_groups) return "norm_groups must divide heads * vdim" + at;
+    } else if (l.mixer == HB_MIXER_MLSTM) {
+      if (l.dim > 256) return "matrix-memory key channels per head > 256 unsupported" + at;
+      if (!(l.gate_cap > 0.f)) return "gate_cap must be positive" + at;
     } else {
       return "unknown mixer" + at;
+    }
+    if (l.mixer == HB_MIXER_GQA) {
+      if ((l.attn_flags & HB_ATTN_QKV_CONV) && (l.conv_taps < 1 || l.conv_taps > 16)) return "convolution taps must be 1..16" + at;
+      if ((l.attn_flags & HB_ATTN_QKV_CONV) && (l.attn_flags & (HB_ATTN_QK_PROJ_NORM | HB_ATTN_V_BLEND | HB_ATTN_V_IS_K)))
+        return "convolved projections with a whole-projection norm, blended values or values that are the keys are unsupported" + at;
+      if ((l.attn_flags & HB_ATTN_OUT_GATE) && (l.attn_flags & HB_ATTN_HEAD_GATE)) return "two output gates" + at;
+    }
+    if (l.side_heads < 0) return "negative side_heads" + at;
+    if (l.side_heads > 0) {
+      if (l.mixer != HB_MIXER_GQA) return "a second mixer stands beside a grouped-query mixer only" + at;
+      if (l.side_mixer != HB_MIXER_MLSTM) return "the second mixer must be a matrix memory" + at;
+      if (l.side_dim <= 0 || l.side_vdim <= 0 || l.side_dim > 256) return "second mixer head sizes" + at;
+      if (!(l.side_gate_cap > 0.f)) return "side_gate_cap must be positive" + at;
+      if (l.attn_flags & HB_ATTN_HEAD_GATE) return "a second mixer with a per-head gate on the first is unsupported" + at;
+    }
+    if (l.weights_of < 0 || l.weights_of > i) return "weights_of must name an earlier layer" + at;
+    if (l.weights_of > 0) {
+      hb_layer_desc a = l, b = L[l.weights_of - 1];
+      if (b.weights_of > 0) return "weights_of must name a layer with tensors of its own" + at;
+      a.weights_of = b.weights_of = 0;
+      if (memcmp(&a, &b, sizeof a) != 0) return "a layer that uses another layer's tensors must have its description" + at;
+      if (l.attn_flags & HB_ATTN_V_BLEND) return "shared tensors with blended values are unsupported" + at;
+      if (l.mixer == HB_MIXER_LATENT) return "shared tensors for latent attention are unsupported" + at;
     }
     if (l.ff < 0) return "negative ff" + at;
     if (l.ff > 0) {
@@ -226,13 +258,28 @@ std::string validate_stack(const hb_stack_desc& d, const hb_layer_desc* L) {
           if (l.route_keep * (R / l.route_groups) < l.top_k) return "the kept groups hold fewer outputs than top_k" + at;
         }
         if (l.shared_ff < 0) return "negative shared_ff" + at;
-      } else if (l.ff_kind != HB_FF_CLAMPED && l.ff_kind != HB_FF_GELU_TANH && l.ff_kind != HB_FF_SILU) {
+      } else if (l.ff_kind != HB_FF_CLAMPED && l.ff_kind != HB_FF_GELU_TANH && l.ff_kind != HB_FF_SILU && l.ff_kind != HB_FF_RELU2) {
         return "unknown feed-forward kind" + at;
       }
     }
   }
-  if (d.norm_place != HB_NORM_OF_SUM && d.norm_place != HB_NORM_OF_OUTPUT && d.norm_place != HB_NORM_BOTH_SIDES) return "unknown norm_place";
+  if (d.norm_place != HB_NORM_OF_SUM && d.norm_place != HB_NORM_OF_OUTPUT && d.norm_place != HB_NORM_BOTH_SIDES &&
+      d.norm_place != HB_NORM_PARALLEL)
+    return "unknown norm_place";
+  if (d.norm_place == HB_NORM_PARALLEL) {
+    if (d.norm_kind != HB_NORM_RMS) return "parallel sublayers need RMS norms";
+    for (int i = 0; i < d.n_layers; ++i)
+      if (L[i].ff > 0 && (L[i].ff_kind == HB_FF_MOE || L[i].ff_kind == HB_FF_CLAMPED)) return "parallel sublayers with a mixture or a biased feed-forward are unsupported";
+  }
   if (d.norm_kind != HB_NORM_RMS && d.norm_kind != HB_NORM_TANH) return "unknown norm_kind";
+  for (int i = 0; i < d.n_layers; ++i) {
+    if (L[i].mixer != HB_MIXER_GQA || !(L[i].attn_flags & HB_ATTN_OUT_BIAS)) continue;
+    if (d.norm_kind == HB_NORM_TANH) return "tanh norms with a biased output projection are unsupported";
+    if (d.norm_place != HB_NORM_PARALLEL && L[i].side_heads > 0 && L[i].mix_scale != 0.f && L[i].mix_scale != 1.f)
+      return "a weighted first mixer with a biased output projection needs parallel sublayers";
+  }
+  for (int i = 0; i < d.n_layers; ++i)
+    if (L[i].side_heads > 0 && !(L[i].attn_flags & HB_ATTN_OUT_GATE)) return "a second mixer needs the entry-wise output gate on the first";
   if (d.norm_kind == HB_NORM_TANH && d.norm_place == HB_NORM_OF_SUM) return "tanh norms of the sum are unsupported";
   if (d.norm_kind == HB_NORM_TANH && !d.plain_gains) return "tanh norms store their gains plainly";
   if (d.norm_kind == HB_NORM_TANH)
@@ -245,6 +292,8 @@ std::vector<double> stack_rope_freqs(const hb_layer_desc& l) {
   const int half = l.rope_dims / 2;
   std::vector<double> f(half);
   for (int i = 0; i < half; ++i) f[i] = pow((double)l.rope_base, -2.0 * i / (double)l.rope_dims);
+  if (l.rope_linear > 0.f)
+    for (int i = 0; i < half; ++i) f[i] /= (double)l.rope_linear;
   if (l.rope_factor > 0.f) {
     const double factor = l.rope_factor, lo = l.rope_low, hi = l.rope_high, orig = l.rope_original;
     for (int i = 0; i < half; ++i) {
@@ -269,12 +318,15 @@ static size_t carve_stack(Model* m, const hb_stack_desc& d, const hb_layer_desc*
     off += up(elems * es);
     return p;
   };
+  bool muted = false;  // a layer that uses another layer's tensors lays out nothing of its own
+  size_t put_ld = 0;   // destination row stride of the next placements (0: rows are contiguous)
   auto put = [&](const std::string& name, uint8_t* dst, size_t row_off, size_t rows, size_t cols, bool gain = false, float fill = 1.f,
                  bool bias = false, int mode = 0) {
-    if (!m) return;
+    if (!m || muted) return;
     Placement p;
     p.mode = mode;
-    p.dst = reinterpret_cast<bf16*>(dst ? dst + row_off * cols * es : nullptr);
+    p.ld = put_ld;
+    p.dst = reinterpret_cast<bf16*>(dst ? dst + row_off * (put_ld ? put_ld : cols) * es : nullptr);
     p.rows = rows;
     p.cols = cols;
     p.is_norm_gain = gain;
@@ -314,9 +366,81 @@ static size_t carve_stack(Model* m, const hb_stack_desc& d, const hb_layer_desc*
     const std::string p = "l" + std::to_string(i) + ".";
     StackLayerW w;
     const size_t H = l.heads, Dk = l.dim, Dv = l.vdim;
+    const bool shared_w = l.weights_of > 0;
+    const size_t off_before = off;
+    muted = shared_w;
     w.norm1 = norm_block(p + "norm1");
     if (both) w.norm1b = norm_block(p + "norm1b");
-    if (l.mixer == HB_MIXER_DELTA) {
+    // a matrix memory: rows [q | k | v | g | i | f] from row `row0` of the fused projection `in`, gate biases in `bias`
+    auto carve_mlstm = [&](const std::string& pm, uint8_t* in, uint8_t* bias, size_t row0, size_t Hm, size_t Dm, size_t Dvm, float cap) {
+      MlstmW& q = w.ml;
+      q.H = (int)Hm; q.D = (int)Dm; q.Dv = (int)Dvm; q.cap = cap;
+      q.off_q = (int)row0;
+      q.off_k = q.off_q + (int)(Hm * Dm);
+      q.off_v = q.off_k + (int)(Hm * Dm);
+      q.off_g = q.off_v + (int)(Hm * Dvm);
+      q.off_i = q.off_g + (int)(Hm * Dvm);
+      q.off_f = q.off_i + (int)Hm;
+      put(pm + "q", in, q.off_q, Hm * Dm, W);
+      put(pm + "k", in, q.off_k, Hm * Dm, W);
+      put(pm + "v", in, q.off_v, Hm * Dvm, W);
+      put(pm + "g", in, q.off_g, Hm * Dvm, W);
+      put(pm + "i", in, q.off_i, Hm, W);
+      put(pm + "f", in, q.off_f, Hm, W);
+      put(pm + "i.b", bias ? bias + (size_t)q.off_i * es : nullptr, 0, Hm, 1, false, 1.f, true);
+      put(pm + "f.b", bias ? bias + (size_t)q.off_f * es : nullptr, 0, Hm, 1, false, 1.f, true);
+      uint8_t* hn = take(Hm * Dvm);
+      put(pm + "norm", hn, 0, Hm * Dvm, 1, true, 1.f);
+      q.hnorm = hn;
+      if (m) {
+        q.state_off = m->state_floats;
+        q.n_off = q.state_off + Hm * Dm * Dvm;
+        q.m_off = q.n_off + Hm * Dm;
+        m->state_floats += Hm * Dm * Dvm + Hm * Dm + Hm;
+        m->state_floats = (m->state_floats + 3) & ~size_t(3);
+      }
+      return (size_t)q.off_f + Hm - row0;  // rows taken
+    };
+    if (l.mixer == HB_MIXER_MAMBA2) {
+      const size_t G = l.kv_heads, N = Dk, inner = H * Dv, C = inner + 2 * G * N, taps = l.conv_taps;
+      w.off_g = 0;                       // z
+      w.off_v = (int)inner;              // x
+      w.off_k = (int)(2 * inner);        // B
+      w.off_q = (int)(2 * inner + G * N);  // C
+      w.off_a = (int)(2 * inner + 2 * G * N);  // dt
+      w.n_in = w.off_a + (int)H;
+      uint8_t* in = take((size_t)w.n_in * W);
+      w.w_in = in;
+      put(p + "mix.in", in, 0, (size_t)w.n_in, W);
+      uint8_t* cw = take(C * taps);
+      uint8_t* cb = take(C);
+      put(p + "mix.conv", cw, 0, C, taps);
+      put(p + "mix.conv.b", cb, 0, C, 1, false, 1.f, true);
+      uint8_t* adt = take(3 * H);
+      put(p + "mix.A_log", adt, 0, H, 1, false, 1.f, true);
+      put(p + "mix.dt_bias", adt ? adt + H * es : nullptr, 0, H, 1, false, 1.f, true);
+      put(p + "mix.D", adt ? adt + 2 * H * es : nullptr, 0, H, 1, true, 1.f);
+      uint8_t* hn = take(inner);
+      uint8_t* o = take(W * inner);
+      put(p + "mix.norm", hn, 0, inner, 1, true, 1.f);
+      put(p + "mix.o", o, 0, W, inner);
+      w.conv_w = cw; w.conv_b = cb; w.a_dt = adt; w.hnorm = hn; w.wo = o; w.o_cols = (int)inner;
+      if (m) {
+        w.state_off = m->state_floats;
+        w.tail_off = w.state_off + H * N * Dv;
+        m->state_floats += H * N * Dv + (taps - 1) * C;
+        m->state_floats = (m->state_floats + 3) & ~size_t(3);
+      }
+    } else if (l.mixer == HB_MIXER_MLSTM) {
+      const size_t rows = 2 * H * Dk + 2 * H * Dv + 2 * H;
+      uint8_t* in = take(rows * W);
+      uint8_t* b = take(rows);
+      w.w_in = in; w.b_in = b; w.n_in = (int)rows;
+      carve_mlstm(p + "mix.", in, b, 0, H, Dk, Dv, l.gate_cap);
+      uint8_t* o = take(W * H * Dv);
+      put(p + "mix.o", o, 0, W, H * Dv);
+      w.wo = o; w.o_cols = (int)(H * Dv);
+    } else if (l.mixer == HB_MIXER_DELTA) {
       const size_t G = l.kv_heads, C = 2 * G * Dk + H * Dv, taps = l.conv_taps;
       w.off_q = 0;
       w.off_k = (int)(G * Dk);
@@ -381,34 +505,55 @@ static size_t carve_stack(Model* m, const hb_stack_desc& d, const hb_layer_desc*
     } else if (l.mixer == HB_MIXER_GQA) {
       const size_t G = l.kv_heads;
       const bool own_v = !(l.attn_flags & HB_ATTN_V_IS_K), gated = (l.attn_flags & HB_ATTN_HEAD_GATE) != 0;
+      const bool out_gate = (l.attn_flags & HB_ATTN_OUT_GATE) != 0, side = l.side_heads > 0;
+      const std::string pm = p + (side ? "mix.left." : "mix.");  // with a second mixer the first one's tensors are mix.left.*
       w.off_q = 0;
       w.off_k = (int)(H * Dk);
       w.off_v = own_v ? (int)(H * Dk + G * Dk) : w.off_k;
       w.off_g = (int)(H * Dk + G * Dk + (own_v ? G * Dv : 0));
-      w.n_in = w.off_g + (gated ? (int)H : 0);
+      w.n_in = w.off_g + (gated ? (int)H : 0) + (out_gate ? (int)(H * Dv) : 0);
+      const size_t first_rows = (size_t)w.n_in;
+      if (side) w.n_in += (int)(2 * (size_t)l.side_heads * l.side_dim + 2 * (size_t)l.side_heads * l.side_vdim + 2 * (size_t)l.side_heads);
       uint8_t* in = take((size_t)w.n_in * W);
       w.w_in = in;
-      put(p + "mix.q", in, w.off_q, H * Dk, W);
-      put(p + "mix.k", in, w.off_k, G * Dk, W);
-      if (own_v) put(p + "mix.v", in, w.off_v, G * Dv, W);
-      if (gated) put(p + "mix.g", in, w.off_g, H, W);
-      if (l.attn_flags & HB_ATTN_QKV_BIAS) {
+      put(pm + "q", in, w.off_q, H * Dk, W);
+      put(pm + "k", in, w.off_k, G * Dk, W);
+      if (own_v) put(pm + "v", in, w.off_v, G * Dv, W);
+      if (gated) put(pm + "g", in, w.off_g, H, W);
+      if (out_gate) put(pm + "g", in, w.off_g, H * Dv, W);
+      if ((l.attn_flags & HB_ATTN_QKV_BIAS) || side) {
         uint8_t* b = take((size_t)w.n_in);
         w.b_in = b;
-        put(p + "mix.q.b", b ? b + (size_t)w.off_q * es : nullptr, 0, H * Dk, 1, false, 1.f, true);
-        put(p + "mix.k.b", b ? b + (size_t)w.off_k * es : nullptr, 0, G * Dk, 1, false, 1.f, true);
-        if (own_v) put(p + "mix.v.b", b ? b + (size_t)w.off_v * es : nullptr, 0, G * Dv, 1, false, 1.f, true);
+        if (l.attn_flags & HB_ATTN_QKV_BIAS) {
+          put(pm + "q.b", b ? b + (size_t)w.off_q * es : nullptr, 0, H * Dk, 1, false, 1.f, true);
+          put(pm + "k.b", b ? b + (size_t)w.off_k * es : nullptr, 0, G * Dk, 1, false, 1.f, true);
+          if (own_v) put(pm + "v.b", b ? b + (size_t)w.off_v * es : nullptr, 0, G * Dv, 1, false, 1.f, true);
+        }
+      }
+      if (side) carve_mlstm(p + "mix.right.", in, (uint8_t*)w.b_in, first_rows, l.side_heads, l.side_dim, l.side_vdim, l.side_gate_cap);
+      if (l.attn_flags & HB_ATTN_QKV_CONV) {
+        const size_t taps = l.conv_taps, C = H * Dk + G * Dk + G * Dv;
+        uint8_t* cw = take(C * taps);
+        w.conv_w = cw;
+        put(pm + "q.conv", cw, 0, H * Dk, taps);
+        put(pm + "k.conv", cw, H * Dk, G * Dk, taps);
+        put(pm + "v.conv", cw, H * Dk + G * Dk, G * Dv, taps);
+        if (m) {
+          w.tail_off = m->state_floats;
+          m->state_floats += (taps - 1) * C;
+          m->state_floats = (m->state_floats + 3) & ~size_t(3);
+        }
       }
       if (l.attn_flags & HB_ATTN_QK_PROJ_NORM) {
         uint8_t* gn = take((H + G) * Dk);
         w.qk_gain = gn;
-        put(p + "mix.q.norm", gn, 0, H * Dk, 1, true, 1.f);
-        put(p + "mix.k.norm", gn ? gn + H * Dk * es : nullptr, 0, G * Dk, 1, true, 1.f);
+        put(pm + "q.norm", gn, 0, H * Dk, 1, true, 1.f);
+        put(pm + "k.norm", gn ? gn + H * Dk * es : nullptr, 0, G * Dk, 1, true, 1.f);
       }
       if (l.attn_flags & HB_ATTN_LEARNED_SINK) {
         uint8_t* sk = take(H);
         w.sink = sk;
-        put(p + "mix.sink", sk, 0, H, 1, false, 1.f, true);
+        put(pm + "sink", sk, 0, H, 1, false, 1.f, true);
       }
       if (l.attn_flags & HB_ATTN_V_BLEND) {
         bool earlier = false;
@@ -417,12 +562,26 @@ static size_t carve_stack(Model* m, const hb_stack_desc& d, const hb_layer_desc*
         if (earlier) {  // the first blending layer keeps its own values: it has no use for a blend weight
           uint8_t* vm = take(1);
           w.vmix = vm;
-          put(p + "mix.vmix", vm, 0, 1, 1, false, 1.f, true);
+          put(pm + "vmix", vm, 0, 1, 1, false, 1.f, true);
         }
       }
-      uint8_t* o = take(W * H * Dv);
-      put(p + "mix.o", o, 0, W, H * Dv);
-      w.wo = o;
+      // the output projections of both mixers side by side in every row: one product over [first | second] inputs
+      const size_t KL = H * Dv, KR = side ? (size_t)l.side_heads * l.side_vdim : 0;
+      uint8_t* o = take(W * (KL + KR));
+      w.wo = o; w.o_cols = (int)(KL + KR);
+      if (side) {
+        put_ld = KL + KR;
+        put(pm + "o", o, 0, W, KL);
+        put(p + "mix.right.o", o ? o + KL * es : nullptr, 0, W, KR);
+        put_ld = 0;
+      } else {
+        put(pm + "o", o, 0, W, KL);
+      }
+      if (l.attn_flags & HB_ATTN_OUT_BIAS) {
+        uint8_t* ob = take(W);
+        w.o_bias = ob;
+        put(pm + "o.b", ob, 0, W, 1, false, 1.f, true);
+      }
       w.cache_plane = planes++;
       w.cache_plane_v = planes++;
       if (m) {
@@ -507,6 +666,15 @@ static size_t carve_stack(Model* m, const hb_stack_desc& d, const hb_layer_desc*
       put(p + "mlp.down", dn, 0, W, Fn);
       w.gu_packed = packed;
       w.norm2 = n2; w.w_gu = gu; w.w_down = dn;
+    } else if (l.ff > 0 && l.ff_kind == HB_FF_RELU2) {
+      const size_t Fn = l.ff;
+      uint8_t* n2 = norm_block(p + "norm2");
+      if (both) w.norm2b = norm_block(p + "norm2b");
+      uint8_t* up_w = take(Fn * W);
+      uint8_t* dn = take(W * Fn);
+      put(p + "mlp.up", up_w, 0, Fn, W);
+      put(p + "mlp.down", dn, 0, W, Fn);
+      w.norm2 = n2; w.w_gu = up_w; w.w_down = dn;
     } else if (l.ff > 0) {
       const size_t Fn = l.ff;
       uint8_t* n2 = norm_block(p + "norm2");
@@ -523,11 +691,24 @@ static size_t carve_stack(Model* m, const hb_stack_desc& d, const hb_layer_desc*
       put(p + "mlp.down.b", bdn, 0, W, 1, false, 1.f, true);
       w.norm2 = n2; w.w_gu = gu; w.b_gu = bgu; w.w_down = dn; w.b_down = bdn;
     }
+    if (shared_w) {
+      // the tensors are the named layer's; the arena space walked through above is handed back.  What stays the layer's own:
+      // its cache planes and its offsets inside a state slot
+      off = off_before;
+      muted = false;
+      if (m) {
+        StackLayerW o = m->sw[l.weights_of - 1];
+        o.state_off = w.state_off; o.tail_off = w.tail_off;
+        o.cache_plane = w.cache_plane; o.cache_plane_v = w.cache_plane_v;
+        o.ml.state_off = w.ml.state_off; o.ml.n_off = w.ml.n_off; o.ml.m_off = w.ml.m_off;
+        w = o;
+      }
+    }
     if (m) m->sw[i] = w;
   }
   uint8_t* fn = norm_block("final.norm");
-  uint8_t* head = take(V * W);
-  put("head", head, 0, V, W);
+  uint8_t* head = d.tie_head ? embed : take(V * W);
+  if (!d.tie_head) put("head", head, 0, V, W);
   if (m) {
     m->s_final_norm = fn;
     m->s_head = head;

@@ -27,6 +27,16 @@ struct BertLayerW {
 //   GQA:    rows [q | k | v (unless the values are the keys) | g (one row per head, when gated)]
 //   DELTA:  rows [q | k | v | g | b (one row per head) | a (one row per head)]
 // Norms of kind HB_NORM_TANH are blocks [gain (width) | offset (width) | alpha (1)] behind one pointer.
+// A matrix-memory mixer (HB_MIXER_MLSTM) as a layer's only mixer or beside its first one: columns of the layer's fused
+// projection, gain over all heads' entries, float offsets of S [H][D][Dv], n [H][D] and m [H] inside a state slot.
+struct MlstmW {
+  int H = 0, D = 0, Dv = 0;  // H == 0: the layer has none
+  float cap = 0.f;
+  int off_q = 0, off_k = 0, off_v = 0, off_g = 0, off_i = 0, off_f = 0;
+  void* hnorm = nullptr;
+  size_t state_off = 0, n_off = 0, m_off = 0;
+};
+
 struct StackLayerW {
   void *norm1 = nullptr, *norm2 = nullptr;
   void *norm1b = nullptr, *norm2b = nullptr;  // HB_NORM_BOTH_SIDES: the norms of the sublayers' outputs (norm1 / norm2: of their inputs)
@@ -44,6 +54,13 @@ struct StackLayerW {
   void *conv_w = nullptr, *a_dt = nullptr;       // DELTA: [2 kv_heads dim + heads vdim][taps] in q, k, v order; [A_log (heads) | dt_bias (heads)]
   size_t tail_off = 0;                           // DELTA: float offset of the [taps - 1][channels] convolution inputs inside a state slot
   void *w_gu_sh = nullptr, *w_down_sh = nullptr;  // mixture of experts: the unit every token uses, rows [gate | up] and down
+  // MAMBA2: rows [z | x | B | C | dt] of w_in; conv_w [heads vdim + 2 kv_heads dim][taps] and its bias conv_b; a_dt =
+  // [A_log (heads) | dt_bias (heads) | D (heads)]; hnorm [heads vdim]; state_off: S [heads][dim][vdim], tail_off: the convolution's
+  // last inputs.  GQA with convolved projections: conv_w [q | k | v channels][taps], tail_off.
+  void* conv_b = nullptr;
+  MlstmW ml;                 // MLSTM as the only mixer, or the second mixer of the layer
+  void* o_bias = nullptr;    // GQA: bias of the output projection [width]
+  int o_cols = 0;            // columns of wo: the first mixer's heads * vdim (+ the second's, stored behind them in every row)
   void* wo = nullptr;
   void *w_gu = nullptr, *b_gu = nullptr, *w_down = nullptr, *b_down = nullptr;  // feed-forward: rows [gate | up]
   size_t state_off = 0;  // GLA: float offset of this layer's [heads][dim][vdim] block inside a state slot
@@ -65,6 +82,7 @@ struct Placement {
   int mode = 0;                // 0: contiguous copy; 1: gate rows -> tile*256 + r%128; 2: up rows -> tile*256+128 + r%128
   bool is_norm_gain = false;   // random init sets these to 1
   bool is_bias = false;        // random init keeps these small
+  size_t ld = 0;               // row stride of the destination in elements (0: cols, rows are contiguous)
   int elem = 2;                // bytes per arena element (4: layer-list decoders in fp32 mode; payloads are widened on upload)
   float fill = 1.0f;           // random init value of norm gains (0 where the stored gain is an offset from one)
 };

@@ -79,14 +79,17 @@ MIXER_GLA = 0
 MIXER_LATENT = 1
 MIXER_GQA = 2
 MIXER_DELTA = 3
+MIXER_MAMBA2 = 4
+MIXER_MLSTM = 5
 MASK_WINDOW, MASK_CHUNK, MASK_CAUSAL = 0, 1, 2
-FF_CLAMPED, FF_GELU_TANH, FF_MOE, FF_SILU = 0, 1, 2, 3
-NORM_OF_SUM, NORM_OF_OUTPUT, NORM_BOTH_SIDES = 0, 1, 2
+FF_CLAMPED, FF_GELU_TANH, FF_MOE, FF_SILU, FF_RELU2 = 0, 1, 2, 3, 4
+NORM_OF_SUM, NORM_OF_OUTPUT, NORM_BOTH_SIDES, NORM_PARALLEL = 0, 1, 2, 3
 NORM_RMS, NORM_TANH = 0, 1
 ROUTER_SOFTMAX, ROUTER_SIGMOID = 0, 1
 EXPERT_SILU, EXPERT_CLAMPED = 0, 1
 ATTN_QK_UNIT_NORM, ATTN_V_IS_K, ATTN_UNIT_SINK, ATTN_HEAD_GATE = 1, 2, 4, 8
 ATTN_QKV_BIAS, ATTN_QK_PROJ_NORM, ATTN_LEARNED_SINK, ATTN_V_BLEND = 16, 32, 64, 128
+ATTN_QKV_CONV, ATTN_OUT_GATE, ATTN_OUT_BIAS = 256, 512, 1024
 
 
 @dataclass
@@ -130,6 +133,17 @@ class LayerDesc:
     expert_kind: int = EXPERT_SILU
     shared_ff: int = 0         # FF_MOE: a unit every token uses
     shared_limit: float = 0.0
+    weights_of: int = 0        # j + 1: the layer uses layer j's tensors (cache and state stay its own); 0: its own
+    rope_linear: float = 0.0   # GQA: rotation frequencies divided by it; <= 0: off
+    norm_groups: int = 0       # MAMBA2: equal parts of the gated output normed separately
+    gate_cap: float = 0.0      # MLSTM
+    side_mixer: int = 0        # a second mixer beside the first when side_heads > 0 (MIXER_MLSTM)
+    side_heads: int = 0
+    side_dim: int = 0
+    side_vdim: int = 0
+    side_gate_cap: float = 0.0
+    mix_scale: float = 0.0     # weights of the two mixers' outputs; 0 = 1
+    side_scale: float = 0.0
 
     def to_c(self):
         return LayerDescC(self.mixer, self.heads, self.dim, self.vdim, self.tau, self.decay_rank, self.q_rank, self.kv_rank,
@@ -137,7 +151,9 @@ class LayerDesc:
                           self.kv_heads, self.mask, self.attn_flags, self.rope_pairing, self.rope_factor, self.rope_low,
                           self.rope_high, self.rope_original, self.ff_kind, self.experts, self.identity_experts, self.top_k,
                           self.score_cap, self.conv_taps, self.router_kind, self.route_groups, self.route_keep, self.route_renorm,
-                          self.route_scale, self.expert_kind, self.shared_ff, self.shared_limit)
+                          self.route_scale, self.expert_kind, self.shared_ff, self.shared_limit, self.weights_of, self.rope_linear,
+                          self.norm_groups, self.gate_cap, self.side_mixer, self.side_heads, self.side_dim, self.side_vdim,
+                          self.side_gate_cap, self.mix_scale, self.side_scale)
 
 
 @dataclass
@@ -156,6 +172,7 @@ class StackDesc:
     norm_kind: int = NORM_RMS
     embed_scale: float = 0.0   # 0 = 1
     logit_scale: float = 0.0   # 0 = 1
+    tie_head: int = 0          # 1: logits from the embedding table
     arch: int = 2
     unused_tensors: frozenset = frozenset()  # checkpoint tensors the design names but this stack has no use for (skipped at load)
 
@@ -171,7 +188,7 @@ class StackDesc:
         arr = (LayerDescC * len(self.layers))(*[l.to_c() for l in self.layers])
         return StackDescC(self.width, self.vocab, len(self.layers), self.compute_f32, self.norm_eps, self.resid_alpha,
                           self.logit_softcap, self.norm_place, self.embed_norm, self.plain_gains, self.norm_kind, self.embed_scale,
-                          self.logit_scale), arr
+                          self.logit_scale, self.tie_head), arr
 
 
 @dataclass

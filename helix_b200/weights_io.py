@@ -12,7 +12,7 @@ import struct
 import numpy as np
 
 from . import engine as _e
-from .engine import LayerDesc, ModelDesc, StackDesc, bf16_bits, MIXER_GLA, MIXER_LATENT, MIXER_GQA, MIXER_DELTA
+from .engine import LayerDesc, ModelDesc, StackDesc, bf16_bits, MIXER_GLA, MIXER_LATENT, MIXER_GQA, MIXER_DELTA, MIXER_MAMBA2, MIXER_MLSTM
 
 _DT = {"BF16": (np.uint16, 2), "F16": (np.float16, 2), "F32": (np.float32, 4)}
 _IGNORED = ("pooler.", "embeddings.position_ids", "rotary_emb.inv_freq", "cls.", "visual.")  # visual.: the VL tower (not served)
@@ -223,8 +223,55 @@ def latanex_desc(cfg, shapes=None, compute_f32=False):
                      logit_scale=float(cfg.get("logit_scale", 1.0)))
 
 
+def funudra_desc(cfg, shapes=None, compute_f32=False):
+    """config.json of a Funudra checkpoint -> StackDesc: a normed embedding that is also the output matrix; layers whose two
+    sublayers read the same stream through two RMS norms and are added together; state-space layers with scalar decays
+    ("mamba2") and layers of two mixers side by side ("parallel": grouped-query attention with convolved, biased projections,
+    rotation in halves with linearly scaled frequencies, capped scores and an entry-wise output gate, beside a matrix memory
+    with exponential gates); relu-squared feed-forwards; layers that use another layer's tensors.  Every size and every
+    constant that may differ between checkpoints comes from the configuration."""
+    layers = []
+    for i, ly in enumerate(cfg["layers"]):
+        m = ly["mixer"]
+        if ly["type"] == "mamba2":
+            d = LayerDesc(mixer=MIXER_MAMBA2, heads=int(m["heads"]), vdim=int(m["vdim"]), dim=int(m["state"]), kv_heads=int(m["groups"]),
+                          norm_groups=int(m.get("norm_groups") or 1), conv_taps=int(m.get("conv") or 1))
+        elif ly["type"] == "parallel":
+            l, r = m["left"], m["right"]
+            d = LayerDesc(mixer=MIXER_GQA, heads=int(l["heads"]), kv_heads=int(l["kv_heads"]), dim=int(l["dim"]), vdim=int(l["vdim"]),
+                          scale=float(l["scale"]), score_cap=float(l.get("softcap") or 0.0), mask=_e.MASK_CAUSAL, window=0,
+                          attn_flags=_e.ATTN_QKV_BIAS | _e.ATTN_OUT_GATE | _e.ATTN_OUT_BIAS)
+            if l.get("conv"):
+                d.attn_flags |= _e.ATTN_QKV_CONV
+                d.conv_taps = int(l["conv"])
+            rot = l.get("rot")
+            if rot and rot.get("dims"):
+                d.rope_dims, d.rope_base, d.rope_pairing = int(rot["dims"]), float(rot["base"]), 0
+                sc = rot.get("scaling")
+                if sc and sc.get("factor"):
+                    d.rope_linear = float(sc["factor"])
+            d.side_mixer, d.side_heads, d.side_dim, d.side_vdim = MIXER_MLSTM, int(r["heads"]), int(r["dim"]), int(r["vdim"])
+            d.side_gate_cap = float(r["gate_cap"])
+            d.mix_scale, d.side_scale = float(m.get("left_scale", 1.0)), float(m.get("right_scale", 1.0))
+            if d.mix_scale == 0.0 or d.side_scale == 0.0:
+                raise ValueError(f"layer {i}: a mixer weight of zero is not representable (0 means 1)")
+        else:
+            raise ValueError(f"layer {i}: unknown layer type {ly['type']!r}")
+        mlp = ly.get("mlp")
+        if mlp is not None:
+            if mlp.get("kind") != "dense":
+                raise ValueError(f"layer {i}: unsupported feed-forward kind {mlp.get('kind')!r}")
+            d.ff_kind, d.ff = _e.FF_RELU2, int(mlp["ff"])
+        if ly.get("weights_of") is not None:
+            d.weights_of = int(ly["weights_of"]) + 1
+        layers.append(d)
+    return StackDesc(width=int(cfg["width"]), vocab=int(cfg["vocab"]), layers=layers, compute_f32=int(bool(compute_f32)),
+                     norm_eps=float(cfg["norm"]["eps"]), resid_alpha=1.0, logit_softcap=0.0, norm_place=_e.NORM_PARALLEL,
+                     embed_norm=1, plain_gains=1, tie_head=1)
+
+
 # layer-list decoders by config.json "architecture"
-STACK_READERS = {"Risepel": risepel_desc, "Lurepel": lurepel_desc, "Latanex": latanex_desc}
+STACK_READERS = {"Risepel": risepel_desc, "Lurepel": lurepel_desc, "Latanex": latanex_desc, "Funudra": funudra_desc}
 
 
 def desc_from_hf_config(cfg, shapes=None, compute_f32=False):

@@ -46,7 +46,7 @@
 extern "C" {
 #endif
 
-#define HB_ABI_VERSION 5
+#define HB_ABI_VERSION 6
 
 typedef enum hb_status {
   HB_OK = 0,
@@ -145,9 +145,32 @@ typedef struct hb_model_desc {
  *                         S <- g S; S <- S + k (beta (v - S^T k))^T; o = S^T q; per-head RMS norm of o (gain mix.norm) and
  *                         silu gate (mix.g).  State slot: S [heads][dim][vdim] fp32 and the last conv_taps - 1 inputs of
  *                         the three convolutions.
+ *        HB_MIXER_MAMBA2  selective state space layer with one scalar decay per head: one projection mix.in laid out
+ *                         [z (heads vdim) | x (heads vdim) | B (kv_heads dim) | C (kv_heads dim) | dt (heads)], dim = the
+ *                         state size, kv_heads = the groups that share B and C; x, B, C pass a causal convolution over
+ *                         conv_taps tokens (mix.conv, bias mix.conv.b) and silu; dt = softplus(dt + mix.dt_bias);
+ *                         S <- exp(-exp(mix.A_log) dt) S + dt B x^T; y = S^T C + mix.D x per head; y silu(z) is divided
+ *                         by its root mean square in norm_groups equal parts, times mix.norm, then mix.o.  State slot:
+ *                         S [heads][dim][vdim] fp32 and the last conv_taps - 1 inputs of the convolution.
+ *        HB_MIXER_MLSTM   matrix memory with exponential gates: q (times dim^-1/2), k (heads x dim), v (heads x vdim);
+ *                         i = cap tanh((mix.i x + mix.i.b) / cap), f = logsigmoid(cap tanh((mix.f x + mix.f.b) / cap)),
+ *                         cap = gate_cap; running maximum m (starts at 0): m' = max(f + m, i);
+ *                         S <- exp(f + m - m') S + exp(i - m') k v^T, n likewise with k alone;
+ *                         o = S^T q / (max(|n . q|, exp(-m')) + 1e-6); per-head unit RMS, gain mix.norm over all heads'
+ *                         entries, sigmoid(mix.g x), mix.o.  State slot: S [heads][dim][vdim], n [heads][dim], m [heads].
+ *      side_heads > 0: a second mixer of kind side_mixer (HB_MIXER_MLSTM; side_heads / side_dim / side_vdim / side_gate_cap)
+ *      reads the same input beside the first; the layer's mixer output is mix_scale * first + side_scale * second (0 = 1).
+ *      The first mixer's tensors are then mix.left.*, the second's mix.right.*.
+ *      Further HB_MIXER_GQA options: HB_ATTN_QKV_CONV (the biased q / k / v projections pass a causal convolution over
+ *      conv_taps tokens per channel, mix.{q,k,v}.conv, before rotation; the last conv_taps - 1 projected rows live in the
+ *      state slot), HB_ATTN_OUT_GATE (the concatenated heads times sigmoid(mix.g x), one row of mix.g per entry),
+ *      HB_ATTN_OUT_BIAS (mix.o.b), rope_linear > 0 (every rotation frequency divided by it).
+ *      weights_of = j + 1 > 0: the layer has no tensors of its own and uses those of layer j (an earlier layer of equal
+ *      description); its cache planes and its part of the state slot are its own.
  *      Residual step (hb_stack_desc.norm_place): HB_NORM_OF_SUM x <- norm(alpha x + f(x)), HB_NORM_OF_OUTPUT
- *      x <- x + norm(f(x)), or HB_NORM_BOTH_SIDES x <- x + norm_b(f(norm_a(x))) (norm1 / norm1b around the mixer, norm2 /
- *      norm2b around the feed-forward).  norm_kind: HB_NORM_RMS, or HB_NORM_TANH = tanh(alpha x) * w + b with a scalar
+ *      x <- x + norm(f(x)), HB_NORM_BOTH_SIDES x <- x + norm_b(f(norm_a(x))) (norm1 / norm1b around the mixer, norm2 /
+ *      norm2b around the feed-forward), or HB_NORM_PARALLEL x <- x + mixer(norm1(x)) + ff(norm2(x)): both sublayers read
+ *      the same x (RMS norms; HB_FF_RELU2 and the gated units).  norm_kind: HB_NORM_RMS, or HB_NORM_TANH = tanh(alpha x) * w + b with a scalar
  *      alpha and a vector b stored beside the gain as <name>.alpha and <name>.b (no statistic of the row; eps unused).
  *      f = mixer and, when ff > 0, the feed-forward (ff_kind):
  *        HB_FF_CLAMPED    g = min(gate, limit), u = clamp(up, +-limit), y = down(g sigmoid(1.702 g) (u + 1)), with biases
@@ -163,15 +186,17 @@ typedef struct hb_model_desc {
  *                         ff_limit); shared_ff > 0: one more unit of that inner size and kind (limit shared_limit,
  *                         mlp.shared.*) runs for every token and is added.
  *        HB_FF_SILU       y = down(silu(gate) * up), no biases
+ *        HB_FF_RELU2      y = down(relu(up)^2): mlp.up, mlp.down, no gate, no biases
  *      Norm gains are stored as offsets from 1 unless plain_gains.  embed_norm: the embedding row is normed (embed.norm) before
- *      the first layer.  Logits are soft-capped: cap * tanh(z / cap) (cap <= 0: off).  Tensor names: embed[.norm], final.norm,
+ *      the first layer.  tie_head: the logits come from the embedding table (no head tensor).  Logits are soft-capped: cap * tanh(z / cap) (cap <= 0: off).  Tensor names: embed[.norm], final.norm,
  *      head, l<i>.norm1/2[b], l<i>.mix.{q,k,v,g,o,norm,a1,a2,a2.b | dq,dq.norm,uq,dkv,dkv.norm,uk,uv,sink,g,o | q,k,[v,]g,o |
- *      q,k,v,{q,k,v}.conv,b,a,A_log,dt_bias,norm,g,o}, l<i>.mlp.{gate,up,down}[.b] or
+ *      q,k,v,{q,k,v}.conv,b,a,A_log,dt_bias,norm,g,o | in,conv,conv.b,dt_bias,A_log,D,norm,o | q,k,v,g,i,i.b,f,f.b,norm,o},
+ *      l<i>.mlp.{gate,up,down}[.b] or
  *      l<i>.mlp.{router,correction,e<j>.gate,e<j>.up,e<j>.down[,shared.gate,shared.up,shared.down]}. ---- */
-typedef enum hb_mixer { HB_MIXER_GLA = 0, HB_MIXER_LATENT = 1, HB_MIXER_GQA = 2, HB_MIXER_DELTA = 3 } hb_mixer;
+typedef enum hb_mixer { HB_MIXER_GLA = 0, HB_MIXER_LATENT = 1, HB_MIXER_GQA = 2, HB_MIXER_DELTA = 3, HB_MIXER_MAMBA2 = 4, HB_MIXER_MLSTM = 5 } hb_mixer;
 typedef enum hb_mask { HB_MASK_WINDOW = 0, HB_MASK_CHUNK = 1, HB_MASK_CAUSAL = 2 } hb_mask;
-typedef enum hb_ff_kind { HB_FF_CLAMPED = 0, HB_FF_GELU_TANH = 1, HB_FF_MOE = 2, HB_FF_SILU = 3 } hb_ff_kind;
-typedef enum hb_norm_place { HB_NORM_OF_SUM = 0, HB_NORM_OF_OUTPUT = 1, HB_NORM_BOTH_SIDES = 2 } hb_norm_place;
+typedef enum hb_ff_kind { HB_FF_CLAMPED = 0, HB_FF_GELU_TANH = 1, HB_FF_MOE = 2, HB_FF_SILU = 3, HB_FF_RELU2 = 4 } hb_ff_kind;
+typedef enum hb_norm_place { HB_NORM_OF_SUM = 0, HB_NORM_OF_OUTPUT = 1, HB_NORM_BOTH_SIDES = 2, HB_NORM_PARALLEL = 3 } hb_norm_place;
 typedef enum hb_norm_kind { HB_NORM_RMS = 0, HB_NORM_TANH = 1 } hb_norm_kind;
 typedef enum hb_router_kind { HB_ROUTER_SOFTMAX = 0, HB_ROUTER_SIGMOID = 1 } hb_router_kind;
 typedef enum hb_expert_kind { HB_EXPERT_SILU = 0, HB_EXPERT_CLAMPED = 1 } hb_expert_kind;
@@ -183,7 +208,10 @@ enum {
   HB_ATTN_QKV_BIAS = 16,     /* q, k, v = W x + b (mix.q.b, mix.k.b, mix.v.b) */
   HB_ATTN_QK_PROJ_NORM = 32, /* q (and k) divided by the root mean square over all heads' entries, times mix.q.norm (mix.k.norm) */
   HB_ATTN_LEARNED_SINK = 64, /* p_j = exp(s_j) / (exp(sink_h) + sum exp(s_i)), sink_h = mix.sink[h] */
-  HB_ATTN_V_BLEND = 128      /* v <- (1 - l) v + l v_first (mix.vmix; the first such layer of the stack supplies v_first) */
+  HB_ATTN_V_BLEND = 128,     /* v <- (1 - l) v + l v_first (mix.vmix; the first such layer of the stack supplies v_first) */
+  HB_ATTN_QKV_CONV = 256,    /* q, k, v (after their biases) pass a causal convolution over conv_taps tokens per channel */
+  HB_ATTN_OUT_GATE = 512,    /* the concatenated heads times sigmoid(mix.g x) entry by entry (mix.g has heads * vdim rows) */
+  HB_ATTN_OUT_BIAS = 1024    /* the output projection has a bias (mix.o.b) */
 };
 typedef struct hb_layer_desc {
   int32_t mixer;       /* hb_mixer */
@@ -214,7 +242,15 @@ typedef struct hb_layer_desc {
   int32_t expert_kind;              /* hb_expert_kind */
   int32_t shared_ff;                /* HB_FF_MOE: inner size of the unit every token uses; 0: none */
   float shared_limit;               /* its clamp (HB_EXPERT_CLAMPED) */
-  int32_t reserved[6];
+  int32_t weights_of;               /* j + 1: the layer uses the tensors of layer j; 0: its own */
+  float rope_linear;                /* GQA: every rotation frequency is divided by it; <= 0: off */
+  int32_t norm_groups;              /* MAMBA2: equal parts of the gated output that are normed separately (>= 1) */
+  float gate_cap;                   /* MLSTM: cap of the gate pre-activations */
+  int32_t side_mixer;               /* hb_mixer of the second mixer (HB_MIXER_MLSTM) when side_heads > 0 */
+  int32_t side_heads, side_dim, side_vdim;
+  float side_gate_cap;
+  float mix_scale, side_scale;      /* weights of the two mixers' outputs; 0 = 1 */
+  int32_t reserved[5];
 } hb_layer_desc;
 typedef struct hb_stack_desc {
   int32_t width, vocab, n_layers;
@@ -226,7 +262,8 @@ typedef struct hb_stack_desc {
   int32_t norm_kind;   /* hb_norm_kind of the residual-step, embedding and final norms */
   float embed_scale;   /* x = embed[token] * embed_scale; 0 = 1 */
   float logit_scale;   /* logits = head(norm(x)) * logit_scale (before the soft cap); 0 = 1 */
-  int32_t reserved[5];
+  int32_t tie_head;    /* 1: the embedding table is the output matrix (no head tensor) */
+  int32_t reserved[4];
 } hb_stack_desc;
 
 typedef struct hb_sampling {

@@ -26,7 +26,7 @@ def test_library_exports_every_declared_symbol():
     missing = [n for n in sorted(decl) if not hasattr(l, n)]
     assert not missing, missing
     assert decl == set(_lib.SIGNATURES), (decl ^ set(_lib.SIGNATURES))
-    assert l.hb_abi_version() == 5
+    assert l.hb_abi_version() == 6
 
 
 def test_struct_sizes_match_header_layout():

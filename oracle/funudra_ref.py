@@ -19,6 +19,7 @@ keeps a cache and a state of its own.  Logits = embed . rmsnorm(x) * g_f (the em
 Notation: T tokens, W width, H / G query / key-value heads, D / Dv per-head key / value size, N state size.  Nothing here
 is shared with the CUDA path.
 """
+import copy
 import math
 
 import numpy as np
@@ -267,6 +268,10 @@ class FunudraOracle:
                 y, st["layer"][i] = mamba2_mixer(h, p["mix"], ly["mixer"], eps, st["layer"].get(i))
             elif ly["type"] == "parallel":
                 y, st["layer"][i] = parallel_mixer(h, p["mix"], ly["mixer"], eps, pos, st["layer"].get(i))
+            elif ly["type"] == "attention":  # one of the two mixers alone (tensors mix.*): not a layer of the design, a test's tool
+                y, st["layer"][i] = attention_branch(h, p["mix"], ly["mixer"], pos, st["layer"].get(i))
+            elif ly["type"] == "memory":
+                y, st["layer"][i] = memory_branch(h, p["mix"], ly["mixer"], eps, st["layer"].get(i))
             else:
                 raise ValueError(ly["type"])
             if ly.get("mlp"):
@@ -315,7 +320,11 @@ def random_config(width=48, vocab=90, order=(("mamba2", True), ("parallel", True
     """order: (type, has feed-forward) per layer; shared {i: j}: layer i uses layer j's tensors; per_layer {i: mixer dict}."""
     layers = []
     for i, (kind, has_ff) in enumerate(order):
-        mixer = dict(mamba2 or mamba2_cfg()) if kind == "mamba2" else dict(parallel or parallel_cfg())
+        mixer = dict(mamba2 or mamba2_cfg()) if kind == "mamba2" else copy.deepcopy(parallel or parallel_cfg())
+        if kind == "attention":
+            mixer = mixer["left"]
+        elif kind == "memory":
+            mixer = mixer["right"]
         if per_layer and i in per_layer:
             mixer = per_layer[i]
         ly = dict(type=kind, mixer=mixer, mlp=dict(kind="dense", ff=ff) if has_ff else None)
@@ -348,27 +357,30 @@ def random_state_dict(cfg, seed=0):
             sd[p + "mix.norm"] = _t(seed, p + "hn", (inner,), 0.1, 1.0)
             sd[p + "mix.o"] = _t(seed, p + "o", (W, inner), s(inner))
         else:
-            l, r = m["left"], m["right"]
-            H, G, D, Dv = l["heads"], l["kv_heads"], l["dim"], l["vdim"]
-            for n, rows in (("q", H * D), ("k", G * D), ("v", G * Dv)):
-                sd[p + f"mix.left.{n}"] = _t(seed, p + "l" + n, (rows, W), 1.5 * s(W))
-                sd[p + f"mix.left.{n}.b"] = _t(seed, p + "l" + n + "b", (rows,), 0.2)
-                if l.get("conv"):
-                    sd[p + f"mix.left.{n}.conv"] = _t(seed, p + "l" + n + "c", (rows, l["conv"]), 0.5)
-            sd[p + "mix.left.g"] = _t(seed, p + "lg", (H * Dv, W), 1.5 * s(W))
-            sd[p + "mix.left.o"] = _t(seed, p + "lo", (W, H * Dv), s(H * Dv))
-            sd[p + "mix.left.o.b"] = _t(seed, p + "lob", (W,), 0.1)
-            H, D, Dv = r["heads"], r["dim"], r["vdim"]
-            sd[p + "mix.right.q"] = _t(seed, p + "rq", (H * D, W), 1.5 * s(W))
-            sd[p + "mix.right.k"] = _t(seed, p + "rk", (H * D, W), 1.5 * s(W))
-            sd[p + "mix.right.v"] = _t(seed, p + "rv", (H * Dv, W), 1.5 * s(W))
-            sd[p + "mix.right.g"] = _t(seed, p + "rg", (H * Dv, W), 1.5 * s(W))
-            sd[p + "mix.right.o"] = _t(seed, p + "ro", (W, H * Dv), s(H * Dv))
-            sd[p + "mix.right.norm"] = _t(seed, p + "rn", (H * Dv,), 0.1, 1.0)
-            sd[p + "mix.right.i"] = _t(seed, p + "ri", (H, W), 2.0 * s(W))
-            sd[p + "mix.right.i.b"] = _t(seed, p + "rib", (H,), 0.5)
-            sd[p + "mix.right.f"] = _t(seed, p + "rf", (H, W), 2.0 * s(W))
-            sd[p + "mix.right.f.b"] = _t(seed, p + "rfb", (H,), 0.5, 2.0)
+            if ly["type"] in ("parallel", "attention"):
+                l, q = (m["left"], p + "mix.left.") if ly["type"] == "parallel" else (m, p + "mix.")
+                H, G, D, Dv = l["heads"], l["kv_heads"], l["dim"], l["vdim"]
+                for n, rows in (("q", H * D), ("k", G * D), ("v", G * Dv)):
+                    sd[q + n] = _t(seed, q + n, (rows, W), 1.5 * s(W))
+                    sd[q + n + ".b"] = _t(seed, q + n + "b", (rows,), 0.2)
+                    if l.get("conv"):
+                        sd[q + n + ".conv"] = _t(seed, q + n + "c", (rows, l["conv"]), 0.5)
+                sd[q + "g"] = _t(seed, q + "g", (H * Dv, W), 1.5 * s(W))
+                sd[q + "o"] = _t(seed, q + "o", (W, H * Dv), s(H * Dv))
+                sd[q + "o.b"] = _t(seed, q + "ob", (W,), 0.1)
+            if ly["type"] in ("parallel", "memory"):
+                r, q = (m["right"], p + "mix.right.") if ly["type"] == "parallel" else (m, p + "mix.")
+                H, D, Dv = r["heads"], r["dim"], r["vdim"]
+                sd[q + "q"] = _t(seed, q + "q", (H * D, W), 1.5 * s(W))
+                sd[q + "k"] = _t(seed, q + "k", (H * D, W), 1.5 * s(W))
+                sd[q + "v"] = _t(seed, q + "v", (H * Dv, W), 1.5 * s(W))
+                sd[q + "g"] = _t(seed, q + "g", (H * Dv, W), 1.5 * s(W))
+                sd[q + "o"] = _t(seed, q + "o", (W, H * Dv), s(H * Dv))
+                sd[q + "norm"] = _t(seed, q + "n", (H * Dv,), 0.1, 1.0)
+                sd[q + "i"] = _t(seed, q + "i", (H, W), 2.0 * s(W))
+                sd[q + "i.b"] = _t(seed, q + "ib", (H,), 0.5)
+                sd[q + "f"] = _t(seed, q + "f", (H, W), 2.0 * s(W))
+                sd[q + "f.b"] = _t(seed, q + "fb", (H,), 0.5, 2.0)
         if ly.get("mlp"):
             Fn = ly["mlp"]["ff"]
             sd[p + "norm2"] = _t(seed, p + "n2", (W,), 0.1, 1.0)

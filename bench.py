@@ -16,7 +16,7 @@ cache.  tokens = sessions * (seq + decode).
                  oracle port on all host threads (pinned with threadpoolctl), bounded sample; --cpu-impl hf switches to
                  HF transformers on torch CPU, which measured 30x slower on the GPU box (profiles/r02c_reference_hf.json)
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--workload llama8b|bge|pack|risepel|lurepel|latanex]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--workload llama8b|bge|pack|risepel|lurepel|latanex|funudra]
 """
 import argparse
 import json
@@ -400,9 +400,14 @@ def bench_latanex(args):
     return bench_stack(args, "latanex")
 
 
+def bench_funudra(args):
+    return bench_stack(args, "funudra")
+
+
 def bench_stack(args, family):
-    """--workload risepel | lurepel | latanex: prefill and decode throughput of layer-list decoder stacks of that design
-    (helix_b200.configs.risepel_stack / lurepel_stack / latanex_stack, random
+    """--workload risepel | lurepel | latanex | funudra: prefill and decode throughput of layer-list decoder stacks of that design
+    (helix_b200.configs.risepel_stack / lurepel_stack / latanex_stack / funudra_stack; the Funudra run also times the Latanex
+    stack, the closest design with recurrent layers, at the same sizes; random
     weights, bf16 serving mode) at a few layer sizes, beside a Llama-family model of equal width / depth / feed-forward size
     through the same engine API.  Per size: `sessions` prompts of `seq` tokens + `decode` generated tokens each; tokens/s =
     tokens / device time of the forward passes of each phase; `families` = CUDA-event spans of one profiled pass by kernel
@@ -418,8 +423,12 @@ def bench_stack(args, family):
     for width, layers in sizes:
         ff = 4 * width
         row = {"width": width, "layers": layers, "ff": ff}
-        build = {"risepel": configs.risepel_stack, "lurepel": configs.lurepel_stack, "latanex": configs.latanex_stack}[family]
-        for name, desc in ((family, build(width, layers, ff=ff)), ("llama", configs.llama_like(width, layers, ff))):
+        build = {"risepel": configs.risepel_stack, "lurepel": configs.lurepel_stack, "latanex": configs.latanex_stack,
+                 "funudra": configs.funudra_stack}[family]
+        arms = [(family, build(width, layers, ff=ff)), ("llama", configs.llama_like(width, layers, ff))]
+        if family == "funudra":
+            arms.append(("latanex", configs.latanex_stack(width, layers, ff=ff)))
+        for name, desc in arms:
             e = hb.Engine(hb.EngineConfig(device=0, max_seqs=sessions, max_ctx=seq + decode + 64,
                                           max_batched_tokens=args.max_batched_tokens, use_cuda_graphs=0 if args.no_graphs else 1))
             e.load_random(desc, 3)
@@ -590,8 +599,8 @@ def main():
     ap.add_argument("--mixed-step-tokens", type=int, default=512)
     ap.add_argument("--fixed-total-sessions", type=int, default=256)
     ap.add_argument("--layers", type=int, default=0, help="debug: truncate the model (INVALID as a bench number)")
-    ap.add_argument("--workload", default="llama8b", choices=["llama8b", "bge", "pack", "risepel", "lurepel", "latanex"])
-    ap.add_argument("--risepel-sizes", nargs="*", default=[], help="risepel / lurepel / latanex workloads: WIDTHxLAYERS ... (default 1024x12 2048x12 4096x6)")
+    ap.add_argument("--workload", default="llama8b", choices=["llama8b", "bge", "pack", "risepel", "lurepel", "latanex", "funudra"])
+    ap.add_argument("--risepel-sizes", nargs="*", default=[], help="risepel / lurepel / latanex / funudra workloads: WIDTHxLAYERS ... (default 1024x12 2048x12 4096x6)")
     ap.add_argument("--chunks", type=int, default=100000)
     ap.add_argument("--ragged", action="store_true", help="bge workload: chunk lengths U[64,512] instead of 512")
     ap.add_argument("--pack-seconds", type=float, default=8.0)
@@ -605,9 +614,10 @@ def main():
     if args.impl == "reference":
         reference_arm(args, rank, world)
         return
-    if args.workload in ("bge", "pack", "risepel", "lurepel", "latanex"):
+    if args.workload in ("bge", "pack", "risepel", "lurepel", "latanex", "funudra"):
         if rank == 0:
-            {"bge": bench_bge, "pack": bench_pack, "risepel": bench_risepel, "lurepel": bench_lurepel, "latanex": bench_latanex}[args.workload](args)
+            {"bge": bench_bge, "pack": bench_pack, "risepel": bench_risepel, "lurepel": bench_lurepel, "latanex": bench_latanex,
+             "funudra": bench_funudra}[args.workload](args)
         return
 
     import torch

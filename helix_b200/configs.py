@@ -127,6 +127,36 @@ def latanex_stack(width, layers, ff=None, window=1024, experts=16, top=4, groups
                        norm_place=E.NORM_BOTH_SIDES, norm_kind=E.NORM_TANH, plain_gains=1, embed_scale=1.0, logit_scale=0.25)
 
 
+def funudra_stack(width, layers, ff=None, vocab=32768, share=False, compute_f32=False):
+    """A Funudra-design stack at sizes that resemble a served model's layers (random-init benchmarks).  Two of three layers
+    are state-space layers (inner size 2 width in heads of 64 channels, 128 states per channel, eight groups, four-tap
+    convolution, eight norm parts); the middle one of each three has two mixers side by side: grouped-query attention (heads
+    of 128, four query heads per key/value head, four-tap convolutions on q / k / v, half of each head rotated with linearly
+    scaled frequencies, capped scores, entry-wise output gate) and a matrix memory (heads of 64 x 128).  Every layer has a
+    relu-squared feed-forward of size ff on the same stream; the embedding table is the output matrix.  share: the second
+    half of the layers uses the tensors of the first half."""
+    from . import engine as E
+    heads = max(1, width // 128)
+    ff = ff or (width * 4)
+    out = []
+    for i in range(layers):
+        if i % 3 == 1:
+            l = E.LayerDesc(mixer=E.MIXER_GQA, heads=heads, kv_heads=max(1, heads // 4), dim=128, vdim=128, scale=128 ** -0.5,
+                            attn_flags=E.ATTN_QKV_BIAS | E.ATTN_QKV_CONV | E.ATTN_OUT_GATE | E.ATTN_OUT_BIAS, conv_taps=4,
+                            mask=E.MASK_CAUSAL, window=0, score_cap=30.0, rope_dims=64, rope_pairing=0, rope_base=500000.0,
+                            rope_linear=4.0, side_mixer=E.MIXER_MLSTM, side_heads=heads, side_dim=64, side_vdim=128,
+                            side_gate_cap=15.0, mix_scale=0.7, side_scale=0.7)
+        else:
+            mh = max(8, 2 * width // 64)
+            l = E.LayerDesc(mixer=E.MIXER_MAMBA2, heads=mh, vdim=64, dim=128, kv_heads=8, norm_groups=8, conv_taps=4)
+        l.ff_kind, l.ff = E.FF_RELU2, ff
+        if share and i >= (layers + 1) // 2 and (i - (layers + 1) // 2) % 3 == i % 3:
+            l.weights_of = i - (layers + 1) // 2 + 1
+        out.append(l)
+    return E.StackDesc(width=width, vocab=vocab, layers=out, compute_f32=int(compute_f32), norm_eps=1e-5, resid_alpha=1.0,
+                       norm_place=E.NORM_PARALLEL, embed_norm=1, plain_gains=1, tie_head=1)
+
+
 def llama_like(width, layers, ff, vocab=32768):
     """The closest existing decoder at equal width / depth / feed-forward size (comparison arm of the layer-list benchmarks)."""
     heads = max(1, width // 128)

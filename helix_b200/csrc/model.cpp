@@ -235,7 +235,7 @@ std::string validate_stack(const hb_stack_desc& d, const hb_layer_desc* L) {
       if (!(l.side_gate_cap > 0.f)) return "side_gate_cap must be positive" + at;
       if (l.attn_flags & HB_ATTN_HEAD_GATE) return "a second mixer with a per-head gate on the first is unsupported" + at;
     }
-    if (l.weights_of < 0 || l.weights_of > i) return "weights_of must name an earlier layer" + at;
+    if (l.weights_of < 0 || l.weights_of > d.n_layers || l.weights_of == i + 1) return "weights_of must name another layer" + at;
     if (l.weights_of > 0) {
       hb_layer_desc a = l, b = L[l.weights_of - 1];
       if (b.weights_of > 0) return "weights_of must name a layer with tensors of its own" + at;
@@ -696,16 +696,19 @@ static size_t carve_stack(Model* m, const hb_stack_desc& d, const hb_layer_desc*
       // its cache planes and its offsets inside a state slot
       off = off_before;
       muted = false;
-      if (m) {
-        StackLayerW o = m->sw[l.weights_of - 1];
-        o.state_off = w.state_off; o.tail_off = w.tail_off;
-        o.cache_plane = w.cache_plane; o.cache_plane_v = w.cache_plane_v;
-        o.ml.state_off = w.ml.state_off; o.ml.n_off = w.ml.n_off; o.ml.m_off = w.ml.m_off;
-        w = o;
-      }
     }
     if (m) m->sw[i] = w;
   }
+  if (m)
+    for (int i = 0; i < d.n_layers; ++i) {  // the named layer may stand before or behind the one that uses its tensors
+      if (L[i].weights_of <= 0) continue;
+      const StackLayerW w = m->sw[i];
+      StackLayerW o = m->sw[L[i].weights_of - 1];
+      o.state_off = w.state_off; o.tail_off = w.tail_off;
+      o.cache_plane = w.cache_plane; o.cache_plane_v = w.cache_plane_v;
+      o.ml.state_off = w.ml.state_off; o.ml.n_off = w.ml.n_off; o.ml.m_off = w.ml.m_off;
+      m->sw[i] = o;
+    }
   uint8_t* fn = norm_block("final.norm");
   uint8_t* head = d.tie_head ? embed : take(V * W);
   if (!d.tie_head) put("head", head, 0, V, W);

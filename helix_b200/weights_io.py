@@ -263,7 +263,15 @@ def funudra_desc(cfg, shapes=None, compute_f32=False):
                 raise ValueError(f"layer {i}: unsupported feed-forward kind {mlp.get('kind')!r}")
             d.ff_kind, d.ff = _e.FF_RELU2, int(mlp["ff"])
         if ly.get("weights_of") is not None:
-            d.weights_of = int(ly["weights_of"]) + 1
+            j, seen = int(ly["weights_of"]), {i}
+            while cfg["layers"][j].get("weights_of") is not None:  # a layer that itself borrows: follow to the tensors' owner
+                if j in seen:
+                    raise ValueError(f"layer {i}: weights_of runs in a circle")
+                seen.add(j)
+                j = int(cfg["layers"][j]["weights_of"])
+            if j == i:
+                raise ValueError(f"layer {i}: weights_of names the layer itself")
+            d.weights_of = j + 1
         layers.append(d)
     return StackDesc(width=int(cfg["width"]), vocab=int(cfg["vocab"]), layers=layers, compute_f32=int(bool(compute_f32)),
                      norm_eps=float(cfg["norm"]["eps"]), resid_alpha=1.0, logit_softcap=0.0, norm_place=_e.NORM_PARALLEL,

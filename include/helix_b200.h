@@ -165,8 +165,8 @@ typedef struct hb_model_desc {
  *      conv_taps tokens per channel, mix.{q,k,v}.conv, before rotation; the last conv_taps - 1 projected rows live in the
  *      state slot), HB_ATTN_OUT_GATE (the concatenated heads times sigmoid(mix.g x), one row of mix.g per entry),
  *      HB_ATTN_OUT_BIAS (mix.o.b), rope_linear > 0 (every rotation frequency divided by it).
- *      weights_of = j + 1 > 0: the layer has no tensors of its own and uses those of layer j (an earlier layer of equal
- *      description); its cache planes and its part of the state slot are its own.
+ *      weights_of = j + 1 > 0: the layer has no tensors of its own and uses those of layer j (another layer of equal
+ *      description that has its own); its cache planes and its part of the state slot are its own.
  *      Residual step (hb_stack_desc.norm_place): HB_NORM_OF_SUM x <- norm(alpha x + f(x)), HB_NORM_OF_OUTPUT
  *      x <- x + norm(f(x)), HB_NORM_BOTH_SIDES x <- x + norm_b(f(norm_a(x))) (norm1 / norm1b around the mixer, norm2 /
  *      norm2b around the feed-forward), or HB_NORM_PARALLEL x <- x + mixer(norm1(x)) + ff(norm2(x)): both sublayers read

@@ -261,8 +261,10 @@ class FunudraOracle:
         pos = st["pos"] + np.arange(T)
         x = rms_norm(P["embed"][np.asarray(tokens)], P["embed_norm"], eps)
         for i, ly in enumerate(cfg["layers"]):
-            src = ly.get("weights_of")
-            p = P["layers"][i if src is None else int(src)]
+            src = i
+            while cfg["layers"][src].get("weights_of") is not None:  # the tensors' owner may itself stand anywhere in the list
+                src = int(cfg["layers"][src]["weights_of"])
+            p = P["layers"][src]
             h = rms_norm(x, p["norms"]["norm1"], eps)
             if ly["type"] == "mamba2":
                 y, st["layer"][i] = mamba2_mixer(h, p["mix"], ly["mixer"], eps, st["layer"].get(i))

@@ -158,6 +158,18 @@ def test_portions_and_shared_tensors_in_the_oracle():
             if k.startswith(f"l{j}."):
                 sd2[f"l{i}." + k[len(f"l{j}."):]] = v
     assert np.allclose(ref.FunudraOracle(own, sd2).forward(toks), want, atol=1e-12)
+    # the owner of the tensors may stand behind its user, and a user may name another user
+    later = copy.deepcopy(own)
+    later["layers"][0]["weights_of"] = 2
+    later["layers"][3]["weights_of"] = 1
+    sd3 = {k: v for k, v in sd2.items() if not k.startswith(("l0.", "l3."))}
+    assert np.allclose(ref.FunudraOracle(later, sd3).forward(toks), want, atol=1e-12)
+    d = weights_io.desc_from_hf_config(later)
+    assert [l.weights_of for l in d.layers] == [3, 0, 0, 2]
+    chain = copy.deepcopy(cfg)
+    chain["layers"][3]["weights_of"] = 1
+    chain["layers"].append(dict(chain["layers"][3], weights_of=3))
+    assert [l.weights_of for l in weights_io.desc_from_hf_config(chain).layers] == [0, 0, 1, 2, 2]
     # the output matrix is the embedding table, after the final norm
     taps = []
     o.forward(toks, taps=taps)

@@ -82,6 +82,7 @@ CONFIGS = {
     "memory_alone": dict(order=((MEM, False),)),
     "feed_forward_everywhere": dict(order=((PAR, True), (M2, True), (ATT, True), (MEM, True))),
     "shared_tensors": dict(order=((M2, True), (PAR, True), (M2, True), (PAR, True), (M2, True)), shared={2: 0, 3: 1, 4: 0}),
+    "owner_behind_its_users": dict(order=((M2, True), (PAR, True), (M2, True), (PAR, True), (M2, True)), shared={0: 2, 1: 3, 4: 2}),
     "shared_neighbours": dict(order=((PAR, False), (PAR, False), (M2, True), (M2, True)), shared={1: 0, 3: 2}),
     "one_kv_head_one_group": dict(parallel=ref.parallel_cfg(heads=4, kv_heads=1, r_heads=1), mamba2=ref.mamba2_cfg(heads=3, groups=1, norm_groups=1)),
     "no_grouping": dict(parallel=ref.parallel_cfg(heads=3, kv_heads=3), mamba2=ref.mamba2_cfg(heads=4, groups=4, norm_groups=4)),

@@ -428,6 +428,10 @@ def bench_stack(args, family):
         arms = [(family, build(width, layers, ff=ff)), ("llama", configs.llama_like(width, layers, ff))]
         if family == "funudra":
             arms.append(("latanex", configs.latanex_stack(width, layers, ff=ff)))
+        if args.arms:
+            arms = [a for a in arms if a[0] in args.arms.split(",")]
+            if not any(a[0] == family for a in arms):
+                raise SystemExit(f"--arms must keep {family}")
         for name, desc in arms:
             e = hb.Engine(hb.EngineConfig(device=0, max_seqs=sessions, max_ctx=seq + decode + 64,
                                           max_batched_tokens=args.max_batched_tokens, use_cuda_graphs=0 if args.no_graphs else 1))
@@ -600,6 +604,7 @@ def main():
     ap.add_argument("--fixed-total-sessions", type=int, default=256)
     ap.add_argument("--layers", type=int, default=0, help="debug: truncate the model (INVALID as a bench number)")
     ap.add_argument("--workload", default="llama8b", choices=["llama8b", "bge", "pack", "risepel", "lurepel", "latanex", "funudra"])
+    ap.add_argument("--arms", default="", help="layer-list workloads: comma list of the models to time (default: all of the workload's)")
     ap.add_argument("--risepel-sizes", nargs="*", default=[], help="risepel / lurepel / latanex / funudra workloads: WIDTHxLAYERS ... (default 1024x12 2048x12 4096x6)")
     ap.add_argument("--chunks", type=int, default=100000)
     ap.add_argument("--ragged", action="store_true", help="bge workload: chunk lengths U[64,512] instead of 512")

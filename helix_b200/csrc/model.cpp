@@ -709,6 +709,7 @@ static size_t carve_stack(Model* m, const hb_stack_desc& d, const hb_layer_desc*
       o.ml.state_off = w.ml.state_off; o.ml.n_off = w.ml.n_off; o.ml.m_off = w.ml.m_off;
       m->sw[i] = o;
     }
+  if (m) m->state_floats = (m->state_floats + 3) & ~size_t(3);  // slots start on 16-byte boundaries
   uint8_t* fn = norm_block("final.norm");
   uint8_t* head = d.tie_head ? embed : take(V * W);
   if (!d.tie_head) put("head", head, 0, V, W);

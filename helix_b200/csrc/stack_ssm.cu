@@ -13,6 +13,7 @@
 // position 0 starts from zeros inside the kernels (m from 0), so a slot needs no clearing when it changes hands.
 // Everything here is fp32; every sum has a fixed order per output element.
 #include <math.h>
+#include <stdlib.h>
 
 #include <algorithm>
 
@@ -46,6 +47,76 @@ __global__ void __launch_bounds__(256) short_conv_kernel(ConvArgs a) {
   if (a.bias) acc += ldf<WT>((const WT*)a.bias, c);
   if (a.act == 1) acc = acc * sigmoidf_(acc);
   a.out[(size_t)t * a.ldo + c] = acc;
+}
+
+// The same for rows whose pieces start on 16-byte boundaries and up to four taps: thread = four neighbouring channels x kConvRun
+// consecutive tokens, the last TAPS - 1 inputs in registers, so a row is read once per run instead of once per tap.  A run may
+// cross entries: the window is refilled (from the slot or with zeros) wherever an entry starts.
+constexpr int kConvRun = 8;
+__device__ __forceinline__ float4 f4add(const float4& a, const float4& b) { return make_float4(a.x + b.x, a.y + b.y, a.z + b.z, a.w + b.w); }
+template <typename WT, int TAPS>
+__global__ void __launch_bounds__(128) short_conv_run_kernel(ConvArgs a) {
+  const int c = (blockIdx.x * blockDim.x + threadIdx.x) * 4;
+  if (c >= a.C) return;
+  const int tb = blockIdx.y * kConvRun;
+  float w[4][TAPS];
+#pragma unroll
+  for (int e = 0; e < 4; ++e)
+#pragma unroll
+    for (int j = 0; j < TAPS; ++j) w[e][j] = ldf<WT>((const WT*)a.w, (size_t)(c + e) * TAPS + j);
+  float4 ib = make_float4(0.f, 0.f, 0.f, 0.f), cb = ib;
+  if (a.in_bias) {
+    const WT* p = (const WT*)a.in_bias + a.bias_off + c;
+    ib = make_float4(ldf<WT>(p, 0), ldf<WT>(p, 1), ldf<WT>(p, 2), ldf<WT>(p, 3));
+  }
+  if (a.bias) {
+    const WT* p = (const WT*)a.bias + c;
+    cb = make_float4(ldf<WT>(p, 0), ldf<WT>(p, 1), ldf<WT>(p, 2), ldf<WT>(p, 3));
+  }
+  float4 win[TAPS > 1 ? TAPS - 1 : 1];
+  int t0 = 0, t1 = -1;
+  bool fresh = false;
+  const float* tail = nullptr;
+#pragma unroll
+  for (int tt = 0; tt < kConvRun; ++tt) {
+    const int t = tb + tt;
+    if (t >= a.T) break;
+    bool refill = tt == 0;
+    if (t >= t1) {
+      const int b = a.seq_of[t];
+      t0 = a.cu[b]; t1 = a.cu[b + 1];
+      fresh = a.first_pos[b] == 0;
+      tail = a.state + (size_t)a.slots[b] * a.slot_stride + a.tail_off;
+      refill = true;
+    }
+    if (refill) {
+#pragma unroll
+      for (int j = 0; j < TAPS - 1; ++j) {
+        const int tau = t - (TAPS - 1 - j);
+        if (tau >= t0) win[j] = f4add(*reinterpret_cast<const float4*>(a.in + (size_t)tau * a.ldi + a.off + c), ib);
+        else if (!fresh) win[j] = *reinterpret_cast<const float4*>(tail + (size_t)(tau - t0 + TAPS - 1) * a.C + c);
+        else win[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+      }
+    }
+    const float4 x = f4add(*reinterpret_cast<const float4*>(a.in + (size_t)t * a.ldi + a.off + c), ib);
+    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+    for (int j = 0; j < TAPS - 1; ++j) {  // oldest tap first, as the per-channel kernel
+      acc[0] = fmaf(w[0][j], win[j].x, acc[0]); acc[1] = fmaf(w[1][j], win[j].y, acc[1]);
+      acc[2] = fmaf(w[2][j], win[j].z, acc[2]); acc[3] = fmaf(w[3][j], win[j].w, acc[3]);
+    }
+    acc[0] = fmaf(w[0][TAPS - 1], x.x, acc[0]); acc[1] = fmaf(w[1][TAPS - 1], x.y, acc[1]);
+    acc[2] = fmaf(w[2][TAPS - 1], x.z, acc[2]); acc[3] = fmaf(w[3][TAPS - 1], x.w, acc[3]);
+    if (a.bias) { acc[0] += cb.x; acc[1] += cb.y; acc[2] += cb.z; acc[3] += cb.w; }
+    if (a.act == 1) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) acc[e] = acc[e] * sigmoidf_(acc[e]);
+    }
+    *reinterpret_cast<float4*>(a.out + (size_t)t * a.ldo + c) = make_float4(acc[0], acc[1], acc[2], acc[3]);
+#pragma unroll
+    for (int j = 0; j + 1 < TAPS - 1; ++j) win[j] = win[j + 1];
+    if (TAPS > 1) win[TAPS - 2] = x;
+  }
 }
 
 // Thread = one channel of one entry: the slot's last taps - 1 inputs become those behind the entry's last token.
@@ -141,22 +212,23 @@ __device__ __forceinline__ void cpa16(float* smem_dst, const float* gsrc) {
 __device__ __forceinline__ void cpa_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 template <int N> __device__ __forceinline__ void cpa_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
-// Block = (entry, head, 32 value columns), DKP / 16 warps: warp w keeps key channels [16 w, 16 w + 16) of the block's 32
-// state columns in registers (lane = column).  Tokens are staged kRecTch at a time through a cp.async double buffer
-// (q | k | the block's v columns | a, b); every warp leaves its partial dot products in shared memory and the block adds them
-// in warp order once per stage.  The block of the first column slice also carries the normaliser vector: lane l of warp w
-// keeps channel 16 w + (l & 15), the 16 lanes' products are added by a butterfly.
-template <int DKP>
+// Block = (entry, head, 32 NC value columns), DKP / 16 warps: warp w keeps key channels [16 w, 16 w + 16) of the block's
+// state columns in registers (lane = NC neighbouring columns; pairs of neighbouring channels as packed f32x2 operands, so one
+// instruction serves two state elements, and one 16-byte broadcast read of q or k feeds 4 NC of them).  Tokens are staged
+// kRecTch at a time through a cp.async double buffer (q | k | the block's v columns | a, b); every warp leaves its partial dot
+// products in shared memory and the block adds them in warp order once per stage.  The block of the first column slice also
+// carries the normaliser vector: lane l of warp w keeps channel 16 w + (l & 15), the 16 lanes' products are added by a
+// butterfly.
+template <int DKP, int NC>
 __global__ void __launch_bounds__(DKP * 2) lin_recurrence_kernel(LinRecArgs a) {
-  constexpr int KS = DKP / 16;
-  constexpr int per_tok = 2 * DKP + 36, stage_floats = kRecTch * per_tok;
-  extern __shared__ __align__(16) float sm[];  // 2 stages | partial outputs [kRecTch][KS][32] | partial n . q [kRecTch][KS]
+  constexpr int KS = DKP / 16, BC = 32 * NC;
+  constexpr int per_tok = 2 * DKP + BC + 4, stage_floats = kRecTch * per_tok;
+  extern __shared__ __align__(16) float sm[];  // 2 stages | partial outputs [kRecTch][KS][BC] | partial n . q [kRecTch][KS]
   float* obuf = sm + 2 * stage_floats;
-  float* nbuf = obuf + kRecTch * KS * 32;
+  float* nbuf = obuf + kRecTch * KS * BC;
   const int b = blockIdx.x, h = blockIdx.y, kvh = h / (a.H / a.G);
   const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
-  const int c0 = blockIdx.z * 32, j = c0 + lane;
-  const bool live = j < a.Dv;
+  const int c0 = blockIdx.z * BC, j0 = c0 + lane * NC;
   const int t0 = a.cu[b], t1 = a.cu[b + 1];
   const int Dk = a.Dk, i0 = w * 16;
   float* slot = a.state + (size_t)a.slots[b] * a.slot_stride;
@@ -165,11 +237,16 @@ __global__ void __launch_bounds__(DKP * 2) lin_recurrence_kernel(LinRecArgs a) {
   const bool do_n = a.nq != nullptr && blockIdx.z == 0;
   const int nch = i0 + (lane & 15);
   float* nst = slot + a.n_off + (size_t)h * Dk + nch;
-  float S[16];
+  float2 S[NC][8];
 #pragma unroll
-  for (int i = 0; i < 16; ++i) S[i] = (!fresh && live && i0 + i < Dk) ? st[(size_t)(i0 + i) * a.Dv + j] : 0.f;
+  for (int e = 0; e < NC; ++e)
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      auto ld = [&](int ch) { return (!fresh && j0 + e < a.Dv && ch < Dk) ? st[(size_t)ch * a.Dv + j0 + e] : 0.f; };
+      S[e][i] = make_float2(ld(i0 + 2 * i), ld(i0 + 2 * i + 1));
+    }
   float nreg = (do_n && !fresh && nch < Dk) ? *nst : 0.f;
-  for (int e = threadIdx.x; e < 2 * stage_floats; e += blockDim.x) sm[e] = 0.f;  // padded key channels read zeros
+  for (int e = threadIdx.x; e < 2 * stage_floats; e += blockDim.x) sm[e] = 0.f;  // padded key channels and columns read zeros
   __syncthreads();
   const bool vec = ((Dk | a.Dv | (int)a.ldq | (int)a.ldk | (int)a.ldv | a.q_off | a.k_off | a.v_off) & 3) == 0 && ((uintptr_t)a.q & 15) == 0 &&
                    ((uintptr_t)a.k & 15) == 0 && ((uintptr_t)a.v & 15) == 0;
@@ -187,16 +264,18 @@ __global__ void __launch_bounds__(DKP * 2) lin_recurrence_kernel(LinRecArgs a) {
           cpa16(dst + i, sq + i);
           cpa16(dst + DKP + i, sk + i);
         }
-        if (lane < 8 && c0 + lane * 4 < a.Dv) cpa16(dst + 2 * DKP + lane * 4, sv + lane * 4);
+        if (lane < 8 * NC && c0 + lane * 4 < a.Dv) cpa16(dst + 2 * DKP + lane * 4, sv + lane * 4);
       } else {
         for (int i = lane; i < Dk; i += 32) {
           cpa4(dst + i, sq + i);
           cpa4(dst + DKP + i, sk + i);
         }
-        if (c0 + lane < a.Dv) cpa4(dst + 2 * DKP + lane, sv + lane);
+#pragma unroll
+        for (int e = 0; e < NC; ++e)
+          if (c0 + lane + 32 * e < a.Dv) cpa4(dst + 2 * DKP + lane + 32 * e, sv + lane + 32 * e);
       }
-      if (lane == 8) cpa4(dst + 2 * DKP + 32, a.ab + row * a.ldab + h);
-      if (lane == 9) cpa4(dst + 2 * DKP + 33, a.ab + row * a.ldab + a.H + h);
+      if (lane == 8 * NC) cpa4(dst + 2 * DKP + BC, a.ab + row * a.ldab + h);
+      if (lane == 8 * NC + 1) cpa4(dst + 2 * DKP + BC + 1, a.ab + row * a.ldab + a.H + h);
     }
     cpa_commit();
   };
@@ -215,20 +294,32 @@ __global__ void __launch_bounds__(DKP * 2) lin_recurrence_kernel(LinRecArgs a) {
     const float* base = sm + stage * stage_floats;
     for (int tt = 0; tt < nt; ++tt) {
       const float* tk = base + tt * per_tok;
-      const float da = tk[2 * DKP + 32], db = tk[2 * DKP + 33];
-      const float bv = db * tk[2 * DKP + lane];
+      const float2 dab = *reinterpret_cast<const float2*>(tk + 2 * DKP + BC);
+      const float da = dab.x, db = dab.y;
+      const float2 da2 = make_float2(da, da);
+      float2 bv2[NC], oa[NC];
+#pragma unroll
+      for (int e = 0; e < NC; ++e) {
+        const float bv = db * tk[2 * DKP + lane * NC + e];
+        bv2[e] = make_float2(bv, bv);
+        oa[e] = make_float2(0.f, 0.f);
+      }
       const float4* q4 = reinterpret_cast<const float4*>(tk + i0);
       const float4* k4 = reinterpret_cast<const float4*>(tk + DKP + i0);
-      float o0 = 0.f, o1 = 0.f, o2 = 0.f, o3 = 0.f;
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
         const float4 q = q4[i], k = k4[i];
-        S[4 * i + 0] = fmaf(da, S[4 * i + 0], k.x * bv); o0 = fmaf(S[4 * i + 0], q.x, o0);
-        S[4 * i + 1] = fmaf(da, S[4 * i + 1], k.y * bv); o1 = fmaf(S[4 * i + 1], q.y, o1);
-        S[4 * i + 2] = fmaf(da, S[4 * i + 2], k.z * bv); o2 = fmaf(S[4 * i + 2], q.z, o2);
-        S[4 * i + 3] = fmaf(da, S[4 * i + 3], k.w * bv); o3 = fmaf(S[4 * i + 3], q.w, o3);
+        const float2 k01 = make_float2(k.x, k.y), k23 = make_float2(k.z, k.w), q01 = make_float2(q.x, q.y), q23 = make_float2(q.z, q.w);
+#pragma unroll
+        for (int e = 0; e < NC; ++e) {
+          S[e][2 * i] = __ffma2_rn(da2, S[e][2 * i], __fmul2_rn(k01, bv2[e]));
+          oa[e] = __ffma2_rn(S[e][2 * i], q01, oa[e]);
+          S[e][2 * i + 1] = __ffma2_rn(da2, S[e][2 * i + 1], __fmul2_rn(k23, bv2[e]));
+          oa[e] = __ffma2_rn(S[e][2 * i + 1], q23, oa[e]);
+        }
       }
-      obuf[(tt * KS + w) * 32 + lane] = (o0 + o1) + (o2 + o3);
+#pragma unroll
+      for (int e = 0; e < NC; ++e) obuf[(tt * KS + w) * BC + lane * NC + e] = oa[e].x + oa[e].y;
       if (do_n) {
         nreg = fmaf(da, nreg, db * tk[DKP + nch]);
         float pn = nreg * tk[nch];
@@ -238,11 +329,11 @@ __global__ void __launch_bounds__(DKP * 2) lin_recurrence_kernel(LinRecArgs a) {
       }
     }
     __syncthreads();
-    for (int e = threadIdx.x; e < nt * 32; e += blockDim.x) {
-      const int tt = e >> 5, c = e & 31;
+    for (int e = threadIdx.x; e < nt * BC; e += blockDim.x) {
+      const int tt = e / BC, c = e % BC;
       float o = 0.f;
 #pragma unroll
-      for (int ww = 0; ww < KS; ++ww) o += obuf[(tt * KS + ww) * 32 + c];
+      for (int ww = 0; ww < KS; ++ww) o += obuf[(tt * KS + ww) * BC + c];
       if (c0 + c < a.Dv) a.out[(size_t)(tc + tt) * a.ldo + (size_t)h * a.Dv + c0 + c] = fmaf(skip, base[tt * per_tok + 2 * DKP + c], o * a.q_scale);
     }
     if (do_n) {
@@ -256,20 +347,24 @@ __global__ void __launch_bounds__(DKP * 2) lin_recurrence_kernel(LinRecArgs a) {
     __syncthreads();  // the stage and the partial outputs are rewritten in the next iteration
   }
   if (t1 <= t0) return;
-  if (live) {
 #pragma unroll
-    for (int i = 0; i < 16; ++i)
-      if (i0 + i < Dk) st[(size_t)(i0 + i) * a.Dv + j] = S[i];
+  for (int e = 0; e < NC; ++e) {
+    if (j0 + e >= a.Dv) continue;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      if (i0 + 2 * i < Dk) st[(size_t)(i0 + 2 * i) * a.Dv + j0 + e] = S[e][i].x;
+      if (i0 + 2 * i + 1 < Dk) st[(size_t)(i0 + 2 * i + 1) * a.Dv + j0 + e] = S[e][i].y;
+    }
   }
   if (do_n && lane < 16 && nch < Dk) *nst = nreg;
 }
 
-template <int DKP>
+template <int DKP, int NC>
 cudaError_t launch_rec(cudaStream_t s, const LinRecArgs& a) {
-  constexpr int KS = DKP / 16;
-  const size_t smem = (size_t)(2 * kRecTch * (2 * DKP + 36) + kRecTch * KS * 32 + kRecTch * KS) * 4;
-  dim3 grid(a.B, a.H, (a.Dv + 31) / 32);
-  lin_recurrence_kernel<DKP><<<grid, DKP * 2, smem, s>>>(a);
+  constexpr int KS = DKP / 16, BC = 32 * NC;
+  const size_t smem = (size_t)(2 * kRecTch * (2 * DKP + BC + 4) + kRecTch * KS * BC + kRecTch * KS) * 4;
+  dim3 grid(a.B, a.H, (a.Dv + BC - 1) / BC);
+  lin_recurrence_kernel<DKP, NC><<<grid, DKP * 2, smem, s>>>(a);
   return cudaGetLastError();
 }
 
@@ -310,14 +405,35 @@ __global__ void __launch_bounds__(256) gated_group_norm_kernel(const float* __re
   const int t = blockIdx.y, part = blockIdx.x, len = n / parts, c0 = part * len;
   const float* ys = y + (size_t)t * ldy + c0;
   const float* zs = z + (size_t)t * ldz + c0;
+  constexpr int kKeep = 8;  // gated values a thread keeps between the two passes (parts of up to 2048 entries are read once)
+  float keep[kKeep];
   float ss = 0.f;
-  for (int i = threadIdx.x; i < len; i += blockDim.x) {
+#pragma unroll
+  for (int r = 0; r < kKeep; ++r) {
+    const int i = threadIdx.x + r * 256;
+    keep[r] = 0.f;
+    if (i < len) {
+      const float zv = zs[i];
+      keep[r] = ys[i] * (zv * sigmoidf_(zv));
+    }
+    ss = fmaf(keep[r], keep[r], ss);
+  }
+  for (int i = threadIdx.x + kKeep * 256; i < len; i += blockDim.x) {
     const float zv = zs[i], u = ys[i] * (zv * sigmoidf_(zv));
     ss = fmaf(u, u, ss);
   }
   ss = block_sum(ss, red);
   const float rs = 1.f / sqrtf(ss / (float)len + eps);
-  for (int i = threadIdx.x; i < len; i += blockDim.x) {
+#pragma unroll
+  for (int r = 0; r < kKeep; ++r) {
+    const int i = threadIdx.x + r * 256;
+    if (i >= len) break;
+    const float v = keep[r] * rs * ldf<WT>(w, c0 + i);
+    const size_t d = (size_t)t * n + c0 + i;
+    if (out) out[d] = v;
+    if (outb) outb[d] = __float2bfloat16(v);
+  }
+  for (int i = threadIdx.x + kKeep * 256; i < len; i += blockDim.x) {
     const float zv = zs[i], u = ys[i] * (zv * sigmoidf_(zv));
     const float v = u * rs * ldf<WT>(w, c0 + i);
     const size_t d = (size_t)t * n + c0 + i;
@@ -396,11 +512,16 @@ __global__ void relu2_b16_kernel(const bf16* __restrict__ in, long ldi, bf16* __
 cudaError_t stack_ssm_init() {
   cudaError_t e;
 #define HB_SMEM(k, n) if ((e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, n)) != cudaSuccess) return e
-  HB_SMEM(lin_recurrence_kernel<16>, 64 * 1024);
-  HB_SMEM(lin_recurrence_kernel<32>, 64 * 1024);
-  HB_SMEM(lin_recurrence_kernel<64>, 64 * 1024);
-  HB_SMEM(lin_recurrence_kernel<128>, 96 * 1024);
-  HB_SMEM(lin_recurrence_kernel<256>, 160 * 1024);
+  HB_SMEM((lin_recurrence_kernel<16, 1>), 64 * 1024);
+  HB_SMEM((lin_recurrence_kernel<32, 1>), 64 * 1024);
+  HB_SMEM((lin_recurrence_kernel<64, 1>), 64 * 1024);
+  HB_SMEM((lin_recurrence_kernel<128, 1>), 96 * 1024);
+  HB_SMEM((lin_recurrence_kernel<256, 1>), 160 * 1024);
+  HB_SMEM((lin_recurrence_kernel<16, 2>), 64 * 1024);
+  HB_SMEM((lin_recurrence_kernel<32, 2>), 64 * 1024);
+  HB_SMEM((lin_recurrence_kernel<64, 2>), 96 * 1024);
+  HB_SMEM((lin_recurrence_kernel<128, 2>), 128 * 1024);
+  HB_SMEM((lin_recurrence_kernel<256, 2>), 200 * 1024);
   HB_SMEM(parallel_step_kernel<float>, 200 * 1024);
   HB_SMEM(parallel_step_kernel<bf16>, 200 * 1024);
 #undef HB_SMEM
@@ -410,6 +531,16 @@ cudaError_t stack_ssm_init() {
 cudaError_t short_conv(cudaStream_t s, const ConvArgs& a) {
   if (a.T <= 0 || a.C <= 0) return cudaSuccess;
   if (a.taps < 1 || a.taps - 1 > kMaxConvTail) return cudaErrorInvalidValue;
+  const bool vec = a.taps <= 4 && ((a.C | (int)a.ldi | a.off | (int)a.ldo | (int)a.slot_stride | (int)a.tail_off) & 3) == 0 &&
+                   ((uintptr_t)a.in & 15) == 0 && ((uintptr_t)a.out & 15) == 0 && ((uintptr_t)a.state & 15) == 0;
+  if (vec) {
+    dim3 g((a.C / 4 + 127) / 128, (a.T + kConvRun - 1) / kConvRun);
+#define HB_CONV(WT, TP) short_conv_run_kernel<WT, TP><<<g, 128, 0, s>>>(a)
+    if (a.f32) { if (a.taps == 1) HB_CONV(float, 1); else if (a.taps == 2) HB_CONV(float, 2); else if (a.taps == 3) HB_CONV(float, 3); else HB_CONV(float, 4); }
+    else { if (a.taps == 1) HB_CONV(bf16, 1); else if (a.taps == 2) HB_CONV(bf16, 2); else if (a.taps == 3) HB_CONV(bf16, 3); else HB_CONV(bf16, 4); }
+#undef HB_CONV
+    return cudaGetLastError();
+  }
   dim3 grid((a.C + 255) / 256, a.T);
   if (a.f32) short_conv_kernel<float><<<grid, 256, 0, s>>>(a);
   else short_conv_kernel<bf16><<<grid, 256, 0, s>>>(a);
@@ -443,11 +574,21 @@ cudaError_t exp_gate_scan(cudaStream_t s, const GateScanArgs& a) {
 cudaError_t lin_recurrence(cudaStream_t s, const LinRecArgs& a) {
   if (a.B <= 0) return cudaSuccess;
   if (a.G <= 0 || a.H % a.G || a.Dk > 256 || a.Dk <= 0) return cudaErrorInvalidValue;
-  if (a.Dk <= 16) return launch_rec<16>(s, a);
-  if (a.Dk <= 32) return launch_rec<32>(s, a);
-  if (a.Dk <= 64) return launch_rec<64>(s, a);
-  if (a.Dk <= 128) return launch_rec<128>(s, a);
-  return launch_rec<256>(s, a);
+  // two columns per lane (blocks of 64 columns) halve the shared-memory reads per product; heads of up to 32 value columns
+  // keep one.  HB_REC_COLS=1 forces the narrow blocks (A/B measurements)
+  static const bool narrow = [] { const char* e = getenv("HB_REC_COLS"); return e && atoi(e) == 1; }();
+  if (a.Dv > 32 && !narrow) {
+    if (a.Dk <= 16) return launch_rec<16, 2>(s, a);
+    if (a.Dk <= 32) return launch_rec<32, 2>(s, a);
+    if (a.Dk <= 64) return launch_rec<64, 2>(s, a);
+    if (a.Dk <= 128) return launch_rec<128, 2>(s, a);
+    return launch_rec<256, 2>(s, a);
+  }
+  if (a.Dk <= 16) return launch_rec<16, 1>(s, a);
+  if (a.Dk <= 32) return launch_rec<32, 1>(s, a);
+  if (a.Dk <= 64) return launch_rec<64, 1>(s, a);
+  if (a.Dk <= 128) return launch_rec<128, 1>(s, a);
+  return launch_rec<256, 1>(s, a);
 }
 
 cudaError_t memory_readout(cudaStream_t s, const float* num, long ldnum, const float* nq, long ldn, const float* ab, long ldab,

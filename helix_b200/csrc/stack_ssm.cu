@@ -200,7 +200,6 @@ __global__ void __launch_bounds__(32) exp_gate_scan_kernel(GateScanArgs a) {
 }
 
 // ------------------------------------------------------------------ the recurrence
-constexpr int kRecTch = 16;  // tokens per shared-memory stage
 __device__ __forceinline__ void cpa4(float* smem_dst, const float* gsrc) {
   const unsigned d = (unsigned)__cvta_generic_to_shared(smem_dst);
   asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(d), "l"(gsrc) : "memory");
@@ -215,12 +214,14 @@ template <int N> __device__ __forceinline__ void cpa_wait() { asm volatile("cp.a
 // Block = (entry, head, 32 NC value columns), DKP / 16 warps: warp w keeps key channels [16 w, 16 w + 16) of the block's
 // state columns in registers (lane = NC neighbouring columns; pairs of neighbouring channels as packed f32x2 operands, so one
 // instruction serves two state elements, and one 16-byte broadcast read of q or k feeds 4 NC of them).  Tokens are staged
-// kRecTch at a time through a cp.async double buffer (q | k | the block's v columns | a, b); every warp leaves its partial dot
+// 16 / NC at a time through a cp.async double buffer (q | k | the block's v columns | a, b); every warp leaves its partial dot
 // products in shared memory and the block adds them in warp order once per stage.  The block of the first column slice also
 // carries the normaliser vector: lane l of warp w keeps channel 16 w + (l & 15), the 16 lanes' products are added by a
 // butterfly.
 template <int DKP, int NC>
-__global__ void __launch_bounds__(DKP * 2) lin_recurrence_kernel(LinRecArgs a) {
+__global__ void __launch_bounds__(DKP * 2, 512 / DKP) lin_recurrence_kernel(LinRecArgs a) {
+  // (64 registers per thread and four 256-thread blocks per SM: a step of 8 sequences x 64 heads x 64 columns is one wave)
+  constexpr int kRecTch = 16 / NC;  // tokens per shared-memory stage
   constexpr int KS = DKP / 16, BC = 32 * NC;
   constexpr int per_tok = 2 * DKP + BC + 4, stage_floats = kRecTch * per_tok;
   extern __shared__ __align__(16) float sm[];  // 2 stages | partial outputs [kRecTch][KS][BC] | partial n . q [kRecTch][KS]
@@ -361,7 +362,7 @@ __global__ void __launch_bounds__(DKP * 2) lin_recurrence_kernel(LinRecArgs a) {
 
 template <int DKP, int NC>
 cudaError_t launch_rec(cudaStream_t s, const LinRecArgs& a) {
-  constexpr int KS = DKP / 16, BC = 32 * NC;
+  constexpr int KS = DKP / 16, BC = 32 * NC, kRecTch = 16 / NC;
   const size_t smem = (size_t)(2 * kRecTch * (2 * DKP + BC + 4) + kRecTch * KS * BC + kRecTch * KS) * 4;
   dim3 grid(a.B, a.H, (a.Dv + BC - 1) / BC);
   lin_recurrence_kernel<DKP, NC><<<grid, DKP * 2, smem, s>>>(a);

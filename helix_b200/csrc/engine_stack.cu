@@ -595,8 +595,16 @@ int Engine::forward_stack(int T, int B, const StepLayout& L, const int32_t* extr
   auto par_step = [&](const float* y, const float* y2, const void* bias, float bias_scale, int next) -> cudaError_t {
     const void* w1 = next < sd.n_layers ? model_.sw[next].norm1 : nullptr;
     const void* w2 = next < sd.n_layers && model_.sl[next].ff > 0 ? model_.sw[next].norm2 : nullptr;
-    return parallel_step(stream_, k.x, nullptr, y, y2, bias, bias_scale, w1, w2, f32, sd.norm_eps, y ? k.x : nullptr, k.hn, x16, k.hn2,
-                         f32 ? nullptr : k.x16b, T, W);
+    // the fp32 copies are written only where a product of the next layer reads them (shapes the tensor-core GEMMs do not take)
+    bool h1_f32 = true, h2_f32 = true;
+    if (next < sd.n_layers) {
+      const hb_layer_desc& nl = model_.sl[next];
+      const int n_in = model_.sw[next].n_in;
+      h1_f32 = !stack_tc(n_in, W, W, nl.mixer == HB_MIXER_GQA ? up8(n_in) : k.ld1);
+      h2_f32 = !stack_tc(nl.ff_kind == HB_FF_RELU2 ? nl.ff : 2 * nl.ff, W, W, k.ld1);
+    }
+    return parallel_step(stream_, k.x, nullptr, y, y2, bias, bias_scale, w1, w2, f32, sd.norm_eps, y ? k.x : nullptr, h1_f32 ? k.hn : nullptr, x16,
+                         h2_f32 ? k.hn2 : nullptr, f32 ? nullptr : k.x16b, T, W);
   };
   // the residual step: the norm covers the sum (post-norm stream) or the sublayer's output alone; with norms on both sides
   // the same launch also norms the input of the sublayer that follows (`pre`, null behind the last one)
@@ -658,7 +666,7 @@ int Engine::forward_stack(int T, int B, const StepLayout& L, const int32_t* extr
   // a matrix memory over the columns of the layer's fused projection (row stride ldin): gates and their running maximum,
   // the recurrence, then normalisation, per-head unit RMS, gain, sigmoid gate and `scale` into columns col0.. of the output
   // projection's input (row stride ldout)
-  auto run_memory = [&](const StackLayerW& w, int ldin, int col0, int ldout, float scale) -> int {
+  auto run_memory = [&](const StackLayerW& w, int ldin, int col0, int ldout, float scale, float* out_f32) -> int {
     const MlstmW& q = w.ml;
     GateScanArgs ga{};
     ga.p = k.p1; ga.ldp = ldin; ga.off_i = q.off_i; ga.off_f = q.off_f; ga.bias = w.b_in; ga.f32 = f32; ga.cap = q.cap;
@@ -679,7 +687,7 @@ int Engine::forward_stack(int T, int B, const StepLayout& L, const int32_t* extr
     ra.B = B; ra.H = q.H; ra.G = q.H; ra.Dk = q.D; ra.Dv = q.Dv;
     SPAN(6, 4.0 * T * q.H * q.D * q.Dv, lin_recurrence(stream_, ra));
     SPAN(3, 16.0 * T * q.H * q.Dv, memory_readout(stream_, k.ctx, k.ldctx, k.ab + 3 * q.H, k.ldab, k.ab, k.ldab, k.p1 + q.off_g, ldin, q.hnorm, f32,
-                                                  sd.norm_eps, scale, k.mo, mo16, ldout, col0, T, q.H, q.Dv));
+                                                  sd.norm_eps, scale, out_f32, mo16, ldout, col0, T, q.H, q.Dv));
     return HB_OK;
   };
   SPAN(3, rowb, embed_rows_f32(stream_, tokens, model_.s_embed, f32, k.x, x16, T, W, sd.embed_scale != 0.f ? sd.embed_scale : 1.f));
@@ -700,6 +708,7 @@ int Engine::forward_stack(int T, int B, const StepLayout& L, const int32_t* extr
     // the norm that prepares the input of whatever follows a sublayer (norms on both sides)
     const void* pre_next = i + 1 < sd.n_layers ? model_.sw[i + 1].norm1 : nullptr;
     const int ocols = w.o_cols ? w.o_cols : H * Dv;  // columns of the output projection (both mixers' when there are two)
+    float* mo_f32 = stack_tc(W, ocols, ocols, W) ? nullptr : k.mo;  // the output projection's fp32 input, when it reads one
     if (l.mixer == HB_MIXER_MAMBA2) {
       const int G = l.kv_heads, N = Dk, inner = H * Dv, C = inner + 2 * G * N;
       ConvArgs ca{};
@@ -723,10 +732,10 @@ int Engine::forward_stack(int T, int B, const StepLayout& L, const int32_t* extr
       ra.cu = cu; ra.first_pos = first; ra.slots = sslot;
       ra.B = B; ra.H = H; ra.G = G; ra.Dk = N; ra.Dv = Dv;
       SPAN(6, 4.0 * T * H * N * Dv, lin_recurrence(stream_, ra));
-      SPAN(3, 16.0 * T * inner, gated_group_norm(stream_, k.ctx, k.ldctx, k.p1 + w.off_g, k.ld1, w.hnorm, f32, sd.norm_eps, l.norm_groups, k.mo,
+      SPAN(3, 16.0 * T * inner, gated_group_norm(stream_, k.ctx, k.ldctx, k.p1 + w.off_g, k.ld1, w.hnorm, f32, sd.norm_eps, l.norm_groups, mo_f32,
                                                  mo16, T, inner));
     } else if (l.mixer == HB_MIXER_MLSTM) {
-      rc = run_memory(w, k.ld1, 0, ocols, 1.f);
+      rc = run_memory(w, k.ld1, 0, ocols, 1.f, mo_f32);
       if (rc != HB_OK) return rc;
     } else if (l.mixer == HB_MIXER_DELTA) {
       const int G = l.kv_heads, GD = G * Dk, C = 2 * GD + H * Dv;
@@ -866,11 +875,11 @@ int Engine::forward_stack(int T, int B, const StepLayout& L, const int32_t* extr
         const bool from16 = tc_dec || fused;
         if (l.attn_flags & HB_ATTN_OUT_GATE)
           SPAN(3, 12.0 * T * H * Dv, gate_scale_rows(stream_, from16 ? nullptr : k.ctx, from16 ? k.att16 : nullptr, H * Dv, k.p1 + w.off_g, ldin,
-                                                     mix_scale, k.mo, mo16, ocols, 0, T, H * Dv));
+                                                     mix_scale, mo_f32, mo16, ocols, 0, T, H * Dv));
         else
           return fail(HB_ERR_INVALID, "a second mixer needs the entry-wise output gate on the first");
         if (w.ml.H > 0) {
-          rc = run_memory(w, ldin, H * Dv, ocols, l.side_scale != 0.f ? l.side_scale : 1.f);
+          rc = run_memory(w, ldin, H * Dv, ocols, l.side_scale != 0.f ? l.side_scale : 1.f, mo_f32);
           if (rc != HB_OK) return rc;
         }
       }

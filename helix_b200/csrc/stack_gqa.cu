@@ -94,16 +94,38 @@ __global__ void __launch_bounds__(kPrepWarps * 32) gqa_prep_kernel(GqaPrepArgs a
   }
 }
 
-// The same step for the common layout — neighbouring pairs (2i, 2i+1), head rows that start on 16-byte boundaries, values
-// that are the keys: a lane owns four consecutive entries (two pairs) of a head row in registers; no shared memory, one
-// 16-byte load and one 8- or 16-byte store per lane and row.  One warp per (token, head) unit; D <= 512.
+// The same step for the common layouts — head rows that start on 16-byte boundaries; neighbouring pairs (2i, 2i+1), or halves
+// (i, i + dims/2) with dims a multiple of 8 and at most 128; values that are the keys, or value rows of their own (one more
+// unit per kv head that copies the row): a lane owns four consecutive entries of a head row in registers (with halves the
+// partner entries come from the lane dims/8 away by shuffles); no shared memory, one 16-byte load and one 8- or 16-byte
+// store per lane and row.  One warp per (token, head) unit; D, Dv <= 512.
 template <typename CT>
 __global__ void __launch_bounds__(256) gqa_prep_vec_kernel(GqaPrepArgs a) {
   const int lane = threadIdx.x & 31;
   const unsigned unit = blockIdx.x * 8u + (threadIdx.x >> 5);
-  const unsigned per_tok = a.H + a.G;
+  const bool sep_v = a.v_off != a.k_off;  // value rows of their own: units H + G .. H + 2G copy them into the cache
+  const unsigned per_tok = a.H + a.G + (sep_v ? a.G : 0);
   if (unit >= (unsigned)a.T * per_tok) return;
   const int t = unit / per_tok, u = unit % per_tok;
+  if (u >= a.H + a.G) {
+    const int head = u - a.H - a.G, slot = a.slots ? a.slots[t] : -1;
+    if (slot < 0) return;
+    const float* vs = a.p + (size_t)t * a.ldp + a.v_off + (size_t)head * a.Dv;
+    CT* vrow = (CT*)a.v_cache + (((size_t)(slot / a.page_size) * a.G + head) * a.page_size + slot % a.page_size) * a.Dv;
+    for (int e = 4 * lane; e < a.Dv; e += 128) {
+      const float4 x = *reinterpret_cast<const float4*>(vs + e);
+      if (sizeof(CT) == 4) {
+        *reinterpret_cast<float4*>(reinterpret_cast<float*>(vrow) + e) = x;
+      } else {
+        __nv_bfloat162 lo = __floats2bfloat162_rn(x.x, x.y), hi = __floats2bfloat162_rn(x.z, x.w);
+        uint2 pk;
+        pk.x = *reinterpret_cast<unsigned*>(&lo);
+        pk.y = *reinterpret_cast<unsigned*>(&hi);
+        *reinterpret_cast<uint2*>(reinterpret_cast<bf16*>(vrow) + e) = pk;
+      }
+    }
+    return;
+  }
   const bool isq = u < a.H;
   const int head = isq ? u : u - a.H;
   const int half = a.rope_dims / 2;
@@ -128,17 +150,38 @@ __global__ void __launch_bounds__(256) gqa_prep_vec_kernel(GqaPrepArgs a) {
     if (sizeof(CT) == 4) *reinterpret_cast<float4*>(reinterpret_cast<float*>(row) + e) = x;
     else put16(reinterpret_cast<bf16*>(row), e, x);
   };
-  if (slot >= 0) {  // values: the key projection as it is
+  if (slot >= 0 && !sep_v) {  // values: the key projection as it is
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
       const int e = 4 * lane + 128 * j;
       if (e < a.D) put((CT*)a.v_cache + rowi * a.Dv, e, v[j]);
     }
   }
+  if (a.pairing == 0 && half > 0) {
+    // halves: the rotating entries lie in the first 128 of the row (v[0]); quad `lane` of the first half pairs with quad
+    // lane + half / 4 of the second.  Every lane takes part in the shuffles.
+    const int hq = half / 4;
+    const bool first = lane < hq, second = lane >= hq && lane < 2 * hq;
+    const int partner = first ? lane + hq : lane - hq;
+    const float4 o = v[0];
+    float4 pr;
+    pr.x = __shfl_sync(0xffffffffu, o.x, partner & 31); pr.y = __shfl_sync(0xffffffffu, o.y, partner & 31);
+    pr.z = __shfl_sync(0xffffffffu, o.z, partner & 31); pr.w = __shfl_sync(0xffffffffu, o.w, partner & 31);
+    if (first || second) {
+      const int qi = first ? lane : lane - hq;  // angles 4 qi .. 4 qi + 3
+      const float4 c0 = *reinterpret_cast<const float4*>(a.cs + (size_t)t * a.rope_dims + 8 * qi);      // cos, sin, cos, sin
+      const float4 c1 = *reinterpret_cast<const float4*>(a.cs + (size_t)t * a.rope_dims + 8 * qi + 4);
+      if (first) {  // x cos - y sin, y = the partner's entries
+        v[0] = make_float4(o.x * c0.x - pr.x * c0.y, o.y * c0.z - pr.y * c0.w, o.z * c1.x - pr.z * c1.y, o.w * c1.z - pr.w * c1.w);
+      } else {      // y cos + x sin, x = the partner's entries
+        v[0] = make_float4(o.x * c0.x + pr.x * c0.y, o.y * c0.z + pr.y * c0.w, o.z * c1.x + pr.z * c1.y, o.w * c1.z + pr.w * c1.w);
+      }
+    }
+  }
 #pragma unroll
   for (int j = 0; j < 4; ++j) {
     const int e = 4 * lane + 128 * j;
-    if (e < a.D) {
+    if (e < a.D && a.pairing == 1) {
       // the lane's two pairs are neighbours in the table: cos, sin, cos, sin (rope_dims is even; a 16-byte load when both rotate)
       float c4[4] = {1.f, 0.f, 1.f, 0.f};
       if (e / 2 + 1 < half) {
@@ -160,8 +203,8 @@ __global__ void __launch_bounds__(256) gqa_prep_vec_kernel(GqaPrepArgs a) {
           y = y0 * cs + x0 * sn;
         }
       }
-      ss += v[j].x * v[j].x + v[j].y * v[j].y + v[j].z * v[j].z + v[j].w * v[j].w;
     }
+    if (e < a.D) ss += v[j].x * v[j].x + v[j].y * v[j].y + v[j].z * v[j].z + v[j].w * v[j].w;
   }
   float rs = 1.f;
   if (a.unit_norm) rs = 1.f / sqrtf(warp_sum(ss) / (float)a.D + a.eps);
@@ -646,8 +689,10 @@ cudaError_t gqa_prep(cudaStream_t s, const GqaPrepArgs& a) {
                        ((uintptr_t)a.p & 15) == 0 && ((uintptr_t)a.q & 15) == 0 && ((uintptr_t)a.q_b16 & 7) == 0 &&
                        ((uintptr_t)a.k_cache & 15) == 0 && ((uintptr_t)a.v_cache & 15) == 0 && ((uintptr_t)a.cs & 15) == 0 &&
                        (a.rope_dims & 3) == 0;
-  if (aligned && (a.pairing == 1 || a.rope_dims == 0) && a.v_off == a.k_off && a.Dv == a.D) {
-    const unsigned blocks = (unsigned)(((long)a.T * (a.H + a.G) + 7) / 8);
+  const bool own_v = a.v_off != a.k_off, v_ok = own_v ? ((a.Dv | a.v_off) & 3) == 0 && a.Dv <= 512 : a.Dv == a.D;
+  const bool pairs_ok = a.pairing == 1 || a.rope_dims == 0 || (a.pairing == 0 && a.rope_dims % 8 == 0 && a.rope_dims <= 128);
+  if (aligned && pairs_ok && v_ok) {
+    const unsigned blocks = (unsigned)(((long)a.T * (a.H + a.G + (own_v ? a.G : 0)) + 7) / 8);
     if (a.f32) gqa_prep_vec_kernel<float><<<blocks, 256, 0, s>>>(a);
     else gqa_prep_vec_kernel<bf16><<<blocks, 256, 0, s>>>(a);
     return cudaGetLastError();

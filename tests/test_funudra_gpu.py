@@ -425,7 +425,7 @@ def test_pages_and_slots_are_reused():
     with make_engine(cfg, sd, 1, max_seqs=2, ctx=192, pool=256) as e:  # 4 pages, 2 sequences
         total = e.stats()["kv_pages_total"]
         assert total == 4
-        for rnd in range(4):  # every round reuses the pages and slots the previous one gave back
+        for rnd in range(4):  # every pass reuses the pages and slots the previous one gave back
             a, b = tokens(40 + rnd, 130, cfg["vocab"]), tokens(50 + rnd, 60, cfg["vocab"])
             sa, sb = e.seq_open(), e.seq_open()
             with pytest.raises(hb.HBError):
@@ -531,3 +531,45 @@ def test_runtime_serves_a_checkpoint_folder(tmp_path):
         assert len(out) == 8
     finally:
         rt.stop()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_trace_replay_command(tmp_path, dtype):
+    # bin/trace_run over a checkpoint folder: portions beside single tokens, requests that end and whose pages and slot the
+    # next request takes, steps without wanted rows; the pool holds exactly what the live requests need (64-token pages)
+    import json
+    import os
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    cfg = ref.random_config(vocab=120, order=((PAR, True), (M2, True), (PAR, False), (M2, True)), shared={2: 0, 3: 1})
+    sd = ref.random_state_dict(cfg, seed=61)
+    model = tmp_path / "model"
+    model.mkdir()
+    (model / "config.json").write_text(json.dumps(cfg))
+    weights_io.write_safetensors(model / "model.safetensors", sd)
+    o = ref.FunudraOracle(cfg, sd)
+    seqs = {k: tokens(90 + i, n, cfg["vocab"]) for i, (k, n) in enumerate((("a", 75), ("b", 40), ("c", 66), ("d", 9), ("e", 30)))}
+    want = {k: o.forward(v) for k, v in seqs.items()}
+    steps = [
+        dict(step=0, entries=[dict(id="a", tokens=seqs["a"][:70], want=[0, 63, 64, 69])], end=[]),
+        dict(step=1, entries=[dict(id="a", tokens=seqs["a"][70:71], want=[0]), dict(id="b", tokens=seqs["b"][:38], want=[])], end=[]),
+        dict(step=2, entries=[dict(id="b", tokens=seqs["b"][38:], want=[1]), dict(id="a", tokens=seqs["a"][71:73], want=[0, 1]),
+                              dict(id="c", tokens=seqs["c"][:2], want=[1]), dict(id="d", tokens=seqs["d"], want=[8])], end=["b", "d"]),
+        dict(step=3, entries=[dict(id="c", tokens=seqs["c"][2:], want=[0, 61, 63]), dict(id="a", tokens=seqs["a"][73:], want=[1]),
+                              dict(id="e", tokens=seqs["e"][:29], want=[28])], end=["a"]),
+        dict(step=4, entries=[dict(id="e", tokens=seqs["e"][29:], want=[0])], end=["c", "e"]),
+    ]
+    out = tmp_path / "out"
+    r = subprocess.run([sys.executable, os.path.join(root, "bin", "trace_run"), "--model", str(model), "--dtype", dtype, "--out", str(out),
+                        "--max-tokens", "320"], input="".join(json.dumps(s) + "\n" for s in steps), capture_output=True, text=True, timeout=900)
+    assert r.returncode == 0, r.stderr[-2000:]
+    assert [l for l in r.stdout.splitlines() if l.startswith("done ")] == [f"done {i}" for i in range(5)]
+    at = {k: 0 for k in seqs}
+    for s in steps:
+        rows = []
+        for en in s["entries"]:
+            rows += [want[en["id"]][at[en["id"]] + w] for w in en["want"]]
+            at[en["id"]] += len(en["tokens"])
+        got = np.fromfile(out / f"{s['step']}.f32", dtype="<f4").reshape(len(rows), cfg["vocab"])
+        assert row_err(got, np.stack(rows)).max() < TOL[1 if dtype == "float32" else 0], s["step"]

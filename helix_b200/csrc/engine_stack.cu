@@ -94,8 +94,11 @@ int Engine::load_begin_stack(const hb_stack_desc& sd, const hb_layer_desc* layer
   layers = lv.data();
   const std::string why = validate_stack(sd, layers);
   if (!why.empty()) return fail(HB_ERR_INVALID, "unsupported model description: " + why);
+  // the per-token attention kernel keeps one position's scores in shared memory.  Steps replayed from graphs fix that size at
+  // capture, so a full context has to fit; otherwise each launch is sized by its step's longest context and a sequence that
+  // outgrows the kernel fails in its step, not here
   for (const hb_layer_desc& l : lv)
-    if (l.mixer == HB_MIXER_GQA && gqa_attn_smem(l.dim, l.vdim, l.window) > 200 * 1024)
+    if (l.mixer == HB_MIXER_GQA && gqa_attn_smem(l.dim, l.vdim, cfg_.use_cuda_graphs ? l.window : std::min(l.window, 256)) > 200 * 1024)
       return fail(HB_ERR_INVALID, "unsupported model description: the keys one position sees exceed the attention kernel's shared memory");
   CU(cudaSetDevice(cfg_.device));
   size_t free_b = 0, total_b = 0;
@@ -869,6 +872,11 @@ int Engine::forward_stack(int T, int B, const StepLayout& L, const int32_t* extr
       aa.T = T; aa.H = H; aa.G = G; aa.D = Dk; aa.Dv = Dv; aa.mask = l.mask; aa.window = l.window;
       aa.unit_sink = (l.attn_flags & HB_ATTN_UNIT_SINK) != 0; aa.scale = l.scale;
       aa.softcap = l.score_cap; aa.sink = (l.attn_flags & HB_ATTN_LEARNED_SINK) ? w.sink : nullptr;
+      if (!cfg_.use_cuda_graphs && gqa_attn_smem(Dk, Dv, l.window) > 200 * 1024) {
+        for (const StepEntry& en : step_entries_) aa.longest_ctx = std::max(aa.longest_ctx, en.first + en.n);
+        if (gqa_attn_smem(Dk, Dv, std::min(l.window, (aa.longest_ctx + 255) / 256 * 256)) > 200 * 1024)
+          return fail(HB_ERR_INVALID, "a position sees more keys than the attention kernel's shared memory holds");
+      }
       SPAN(7, 2.0 * T * H * (double)std::min(l.window, cfg_.max_ctx) * (Dk + Dv), gqa_attn(stream_, aa));
       }
       if (post) {

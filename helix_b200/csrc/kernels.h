@@ -423,6 +423,9 @@ struct GqaAttnArgs {
   bool unit_sink; float scale;
   float softcap = 0.f;         // > 0: s <- softcap * tanh(s / softcap) after the scale
   const void* sink = nullptr;  // [H] of the cache element type: exp(sink_h) joins the denominator (instead of unit_sink)
+  // > 0: no position of this launch is beyond longest_ctx - 1, so the scores' shared memory is sized for that many keys instead
+  // of a full context (launches that are not replayed from a graph, whose shared memory is fixed at capture)
+  int longest_ctx = 0;
 };
 cudaError_t gqa_attn(cudaStream_t s, const GqaAttnArgs& a);
 size_t gqa_attn_smem(int D, int Dv, int max_keys);  // dynamic shared memory the kernel needs to see max_keys keys

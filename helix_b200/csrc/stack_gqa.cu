@@ -711,7 +711,8 @@ cudaError_t gqa_attn(cudaStream_t s, const GqaAttnArgs& a) {
   if (a.G <= 0 || a.H % a.G || (a.mask != MASK_CAUSAL && a.window <= 0)) return cudaErrorInvalidValue;
   // the longest run of keys any position of a sequence can see: window / block length, never more than a sequence holds
   const int ctx = a.max_pages * a.page_size;
-  const int max_keys = a.mask == MASK_CAUSAL ? ctx : std::min(a.window, ctx);
+  int max_keys = a.mask == MASK_CAUSAL ? ctx : std::min(a.window, ctx);
+  if (a.longest_ctx > 0) max_keys = std::min(max_keys, (a.longest_ctx + 255) / 256 * 256);  // sized by what this step's positions see
   const size_t smem = gqa_attn_smem(a.D, a.Dv, max_keys);
   if (smem > 200 * 1024) return cudaErrorInvalidValue;
   const int rep = a.H / a.G;

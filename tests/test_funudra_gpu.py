@@ -573,3 +573,17 @@ def test_trace_replay_command(tmp_path, dtype):
             at[en["id"]] += len(en["tokens"])
         got = np.fromfile(out / f"{s['step']}.f32", dtype="<f4").reshape(len(rows), cfg["vocab"])
         assert row_err(got, np.stack(rows)).max() < TOL[1 if dtype == "float32" else 0], s["step"]
+
+
+def test_context_longer_than_the_attention_kernels_shared_memory():
+    # an engine whose context (16384 positions) is more than the per-token attention kernel can keep scores for: launches are
+    # sized by the step's longest context, so sequences of ordinary length run; graph replay needs the full size and is refused
+    cfg = ref.random_config(order=((PAR, True), (M2, False)))
+    sd = ref.random_state_dict(cfg, seed=67)
+    toks = tokens(12, 300, cfg["vocab"])
+    want = ref.FunudraOracle(cfg, sd).forward(toks)
+    for f32 in (1, 0):
+        with make_engine(cfg, sd, f32, ctx=16384, batched=512, pool=1024) as e:
+            assert row_err(replay(e, toks, [200, 2, 90]), want).max() < TOL[f32]
+    with pytest.raises(hb.HBError):
+        make_engine(cfg, sd, 1, ctx=16384, batched=512, pool=1024, use_cuda_graphs=1)

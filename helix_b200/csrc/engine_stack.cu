@@ -1,4 +1,4 @@
-// Layer-list decoders (HB_ARCH_STACK: the Risepel, Lurepel and Latanex designs) inside hb::Engine: model load, the page pool's planes and recurrent state slots,
+// Layer-list decoders (HB_ARCH_STACK: the Risepel, Lurepel, Latanex and Funudra designs) inside hb::Engine: model load, the page pool's planes and recurrent state slots,
 // the step's forward pass and the driven-sequence entry points.  Scheduling, page bookkeeping, the step block, sampling
 // and request records are the engine's own (engine.cu); this file adds what differs from the Llama path:
 //   * the residual stream is fp32 and post-normed; every sublayer reads the stream itself;

@@ -273,7 +273,9 @@ def funudra_desc(cfg, shapes=None, compute_f32=False):
                 raise ValueError(f"layer {i}: weights_of names the layer itself")
             d.weights_of = j + 1
         layers.append(d)
-    return StackDesc(width=int(cfg["width"]), vocab=int(cfg["vocab"]), layers=layers, compute_f32=int(bool(compute_f32)),
+    # a checkpoint may carry the second norm of a layer that has no feed-forward to read it
+    unused = frozenset(f"l{i}.norm2" for i, d in enumerate(layers) if d.ff == 0)
+    return StackDesc(unused_tensors=unused, width=int(cfg["width"]), vocab=int(cfg["vocab"]), layers=layers, compute_f32=int(bool(compute_f32)),
                      norm_eps=float(cfg["norm"]["eps"]), resid_alpha=1.0, logit_softcap=0.0, norm_place=_e.NORM_PARALLEL,
                      embed_norm=1, plain_gains=1, tie_head=1)
 

@@ -210,6 +210,7 @@ def test_configuration_reader_key_by_key():
     assert (b.side_mixer, b.side_heads, b.side_dim, b.side_vdim, b.side_gate_cap) == (E.MIXER_MLSTM, 5, 12, 20, 9.0)
     assert (b.mix_scale, b.side_scale) == (0.4, 1.3)
     assert c.weights_of == 1 and (c.mixer, c.ff) == (a.mixer, a.ff)
+    assert d.unused_tensors == frozenset({"l1.norm2"})  # a second norm stored for a layer without a feed-forward is skipped at load
     # absent keys: no convolution, no rotation, no frequency scaling, no cap
     bare = copy.deepcopy(cfg)
     l = bare["layers"][1]["mixer"]["left"]

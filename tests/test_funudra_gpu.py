@@ -483,6 +483,16 @@ def test_continuous_batching_and_mixed_steps_match_solo_runs():
         assert graphed == solo
 
 
+def test_second_norm_of_a_layer_without_feed_forward_is_skipped():
+    cfg = ref.random_config()  # the last layer has no feed-forward
+    sd = ref.random_state_dict(cfg, seed=71)
+    toks = tokens(13, 40, cfg["vocab"])
+    want = ref.FunudraOracle(cfg, sd).forward(toks)
+    sd["l2.norm2"] = np.full(cfg["width"], 3.0, np.float32)
+    with make_engine(cfg, sd, 1) as e:
+        assert row_err(replay(e, toks, [len(toks)]), want).max() < TOL[1]
+
+
 def test_random_weights_and_rejected_descriptions():
     cfg = ref.random_config()
     desc = weights_io.desc_from_hf_config(cfg)
